@@ -1,0 +1,324 @@
+"""CPU restatement (torch CPU ops + numpy) of the reference TCFP-12 hot path.
+
+TEST INFRASTRUCTURE ONLY -- see ``oracle/__init__.py``.
+
+Every function cites the reference file:line it follows (paths are relative
+to the reference project root).  The per-tensor functions are pinned
+bit-for-bit against the reference itself, imported on CPU, by the golden
+fixtures in ``tests/golden`` (generator: ``tests/golden/make_golden.py``).
+The block-scaled functions restate Triton kernels that cannot execute without
+a GPU; they are pinned by the differential properties the reference's own
+tests assert (fused == two sequential block quantizes, the error-feedback
+formula, sentinel handling) -- parity for those is otherwise UNPINNED.
+
+Conventions: weights ``(N, K)`` row-major, activations ``(M, K)``, block
+exponent planes ``(K // bs, rows)`` int8 with ``-128`` as the zero-residual
+sentinel, per-tensor inverse scales of shape ``(1,)`` float32.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+FP8_E4M3_MAX = 448.0          # tcfp/core.py:29
+FP8_E5M2_MAX = 57344.0        # tcfp/core.py:35
+E4M3 = torch.float8_e4m3fn
+E5M2 = torch.float8_e5m2
+
+
+# ---------------------------------------------------------------------------
+# Philox4x32-10 uniforms: the seed/offset contract of the stochastic paths
+# ---------------------------------------------------------------------------
+
+_PHILOX_KEY_A = np.uint32(0x9E3779B9)
+_PHILOX_KEY_B = np.uint32(0xBB67AE85)
+_PHILOX_ROUND_A = np.uint64(0xD2511F53)
+_PHILOX_ROUND_B = np.uint64(0xCD9E8D57)
+
+
+def philox4x32_10(seed: int, counter: np.ndarray) -> np.ndarray:
+    """First 32-bit output word of Philox4x32-10.
+
+    key = (seed & 2^32-1, seed >> 32); counter words = (ctr & 2^32-1,
+    ctr >> 32, 0, 0).  This is the published Philox algorithm (Salmon et al.,
+    SC'11) with the word order used by ``tl.rand`` (the generator the
+    reference's block kernel draws from, tcfp/kernels.py:415-417).
+    """
+    ctr = np.asarray(counter, dtype=np.uint64)
+    c0 = (ctr & np.uint64(0xFFFFFFFF)).astype(np.uint32)
+    c1 = (ctr >> np.uint64(32)).astype(np.uint32)
+    c2 = np.zeros_like(c0)
+    c3 = np.zeros_like(c0)
+    k0 = np.uint32(seed & 0xFFFFFFFF)
+    k1 = np.uint32((seed >> 32) & 0xFFFFFFFF)
+    with np.errstate(over="ignore"):
+        for _ in range(10):
+            pb = _PHILOX_ROUND_B * c2.astype(np.uint64)
+            pa = _PHILOX_ROUND_A * c0.astype(np.uint64)
+            n0 = (pb >> np.uint64(32)).astype(np.uint32) ^ c1 ^ k0
+            n2 = (pa >> np.uint64(32)).astype(np.uint32) ^ c3 ^ k1
+            n1 = (pb & np.uint64(0xFFFFFFFF)).astype(np.uint32)
+            n3 = (pa & np.uint64(0xFFFFFFFF)).astype(np.uint32)
+            c0, c1, c2, c3 = n0, n1, n2, n3
+            k0 = np.uint32((int(k0) + int(_PHILOX_KEY_A)) & 0xFFFFFFFF)
+            k1 = np.uint32((int(k1) + int(_PHILOX_KEY_B)) & 0xFFFFFFFF)
+    return c0
+
+
+def philox_uniform(seed: int, offset: int, numel: int) -> torch.Tensor:
+    """Uniforms ``u[i] in [0,1)`` for linear element index ``i``.
+
+    ``u[i] = f(philox4x32_10(seed, offset + i))`` where ``f`` reinterprets the
+    word as int32, maps negatives ``x -> -x-1`` and multiplies the
+    int->float32 conversion by 4.6566127342e-10 (the ``tl.rand`` mapping).
+    With ``offset = 0`` and a 31-bit seed these are the numbers the
+    reference's ``_fused_dual_quantize_kernel`` draws for element
+    ``n*K + k`` (tcfp/kernels.py:415-417).
+    """
+    idx = np.arange(numel, dtype=np.uint64) + np.uint64(offset)
+    w = philox4x32_10(seed, idx).view(np.int32).astype(np.int64)
+    w = np.where(w < 0, -w - 1, w)
+    u = w.astype(np.float32) * np.float32(4.6566127342e-10)
+    return torch.from_numpy(u)
+
+
+# ---------------------------------------------------------------------------
+# Per-tensor casts (tcfp/core.py)
+# ---------------------------------------------------------------------------
+
+def _per_tensor_scale(t: torch.Tensor, fmax: float) -> torch.Tensor:
+    # tcfp/core.py:100-101 (and :128-129, :152-153)
+    amax = t.abs().max().clamp(min=1e-12)
+    return (fmax / amax).to(torch.float32)
+
+
+def to_fp8_e4m3(t: torch.Tensor, scale: torch.Tensor | None = None):
+    """tcfp/core.py:85-106."""
+    if scale is None:
+        scale = _per_tensor_scale(t, FP8_E4M3_MAX)
+    scaled = (t.float() * scale).clamp(-FP8_E4M3_MAX, FP8_E4M3_MAX)
+    inv = torch.ones(1, dtype=torch.float32) / scale
+    return scaled.to(E4M3), inv
+
+
+def to_fp8_e5m2(t: torch.Tensor, scale: torch.Tensor | None = None):
+    """tcfp/core.py:137-158."""
+    if scale is None:
+        scale = _per_tensor_scale(t, FP8_E5M2_MAX)
+    scaled = (t.float() * scale).clamp(-FP8_E5M2_MAX, FP8_E5M2_MAX)
+    inv = torch.ones(1, dtype=torch.float32) / scale
+    return scaled.to(E5M2), inv
+
+
+def stochastic_round_to_fp8_e4m3(t: torch.Tensor, rand: torch.Tensor) -> torch.Tensor:
+    """tcfp/core.py:418-464 with the uniforms passed in instead of drawn."""
+    lo = t.to(E4M3)
+    lo_f = lo.float()
+    direction = torch.sign(t - lo_f)
+    exact = t == lo_f
+    nudge = direction * (2.0 ** -6) * 0.5
+    hi = (lo_f + nudge).to(E4M3)
+    same = (hi.float() == lo_f) & ~exact
+    abs_lo = lo_f.abs().clamp(min=2.0 ** -6)
+    hi_retry = (lo_f + direction * abs_lo * 0.25).to(E4M3)
+    hi = torch.where(same, hi_retry, hi)
+    hi_f = hi.float()
+    gap = (hi_f - lo_f).abs().clamp(min=1e-45)
+    frac = ((t - lo_f).abs() / gap).clamp(0.0, 1.0)
+    return torch.where(exact, lo, torch.where(rand < frac, hi, lo))
+
+
+def to_fp8_e4m3_sr(t: torch.Tensor, rand: torch.Tensor, scale: torch.Tensor | None = None):
+    """tcfp/core.py:109-134."""
+    if scale is None:
+        scale = _per_tensor_scale(t, FP8_E4M3_MAX)
+    scaled = (t.float() * scale).clamp(-FP8_E4M3_MAX, FP8_E4M3_MAX)
+    inv = torch.ones(1, dtype=torch.float32) / scale
+    return stochastic_round_to_fp8_e4m3(scaled, rand), inv
+
+
+def dual_quantize_per_tensor(
+    weight: torch.Tensor,
+    error: torch.Tensor | None = None,
+    *,
+    srr: bool = False,
+    seed: int = 0,
+    offset: int = 0,
+    amax_hi: torch.Tensor | None = None,
+    amax_lo: torch.Tensor | None = None,
+):
+    """Steps 1-4 of ``_TCFP12TensorCoreFunction.forward``
+    (tcfp/nn/__init__.py:343-383).
+
+    Returns ``(w_hi, w_lo, inv_hi, inv_lo, new_error, cur_amax_hi,
+    cur_amax_lo)``.  ``amax_hi`` / ``amax_lo`` override the fresh amax the way
+    delayed scaling does (tcfp/nn/__init__.py:282-285, 302-309); the current
+    (pre-clamp) amaxes are returned for the caller's EMA bookkeeping.
+    ``new_error`` is ``None`` without an error buffer.
+    """
+    w = weight.float()
+    if error is not None:
+        w = w + error
+    cur_hi = w.abs().max()
+    s_hi = (FP8_E4M3_MAX / (cur_hi.clamp(min=1e-12) if amax_hi is None else amax_hi)).to(torch.float32)
+    w_hi, inv_hi = to_fp8_e4m3(w, scale=s_hi)
+    residual = w - w_hi.float() * inv_hi
+    cur_lo = residual.abs().max()
+    s_lo = (FP8_E4M3_MAX / (cur_lo.clamp(min=1e-12) if amax_lo is None else amax_lo)).to(torch.float32)
+    if srr:
+        rand = philox_uniform(seed, offset, w.numel()).reshape(w.shape)
+        w_lo, inv_lo = to_fp8_e4m3_sr(residual, rand, scale=s_lo)
+    else:
+        w_lo, inv_lo = to_fp8_e4m3(residual, scale=s_lo)
+    new_error = None
+    if error is not None:
+        recon = w_hi.float() * inv_hi + w_lo.float() * inv_lo
+        new_error = weight.float() - recon
+    return w_hi, w_lo, inv_hi, inv_lo, new_error, cur_hi, cur_lo
+
+
+# ---------------------------------------------------------------------------
+# Block-scaled quantizers (tcfp/kernels.py)
+# ---------------------------------------------------------------------------
+
+def _block_exponent(amax: torch.Tensor, fmax: float) -> torch.Tensor:
+    # tcfp/kernels.py:250-256 (and :367-370, :387-390)
+    raw = torch.ceil(torch.log2(amax.clamp(min=1e-12) / fmax))
+    return raw.clamp(min=-126.0)
+
+
+def block_quantize(x: torch.Tensor, bs: int, fp8_dtype: torch.dtype = E4M3):
+    """``block_quantize_fp8`` / ``_block_quantize_kernel``
+    (tcfp/kernels.py:205-275, 1675-1722).  Returns codes ``(M, K)`` and int8
+    exponents ``(K // bs, M)``."""
+    M, K = x.shape
+    assert K % bs == 0
+    fmax = FP8_E5M2_MAX if fp8_dtype == E5M2 else FP8_E4M3_MAX
+    xb = x.float().reshape(M, K // bs, bs)
+    e = _block_exponent(xb.abs().amax(dim=-1), fmax)
+    q = (xb / torch.exp2(e).unsqueeze(-1)).clamp(-fmax, fmax).to(fp8_dtype)
+    return q.reshape(M, K), e.to(torch.int8).t().contiguous()
+
+
+def block_dequantize(codes: torch.Tensor, exps: torch.Tensor, bs: int) -> torch.Tensor:
+    """``block_dequantize_fp8`` (tcfp/kernels.py:1725-1746)."""
+    M, K = codes.shape
+    scales = torch.exp2(exps.float())
+    return (codes.float().reshape(M, K // bs, bs) * scales.t().unsqueeze(-1)).reshape(M, K)
+
+
+def _sr_block(x: torch.Tensor, rand: torch.Tensor) -> torch.Tensor:
+    """Stochastic rounding of the block kernel (tcfp/kernels.py:398-423)."""
+    # values are clamped to +-448 before the cast; the nudged probe can reach
+    # 560, which the hardware cast saturates to 448 -- clamp to mirror that.
+    rtn = x.to(E4M3)
+    rtn_f = rtn.float()
+    diff = x - rtn_f
+    direction = torch.where(diff >= 0, 1.0, -1.0)
+    abs_rtn = rtn_f.abs().clamp(min=1e-12)
+    nudge = direction * abs_rtn * 0.25
+    other = (rtn_f + nudge).clamp(-FP8_E4M3_MAX, FP8_E4M3_MAX).to(E4M3)
+    other_f = other.float()
+    gap = (other_f - rtn_f).abs().clamp(min=1e-45)
+    frac = (diff.abs() / gap).clamp(max=1.0)
+    boundary = (other_f - rtn_f).abs() < 1e-45
+    exact = (diff.abs() < 1e-45) | boundary
+    return torch.where(exact, rtn, torch.where(rand < frac, other, rtn))
+
+
+def dual_quantize_block(
+    weight: torch.Tensor,
+    bs: int,
+    error: torch.Tensor | None = None,
+    *,
+    srr: bool = False,
+    seed: int = 0,
+    offset: int = 0,
+):
+    """``fused_dual_quantize_fp8`` / ``_fused_dual_quantize_kernel``
+    (tcfp/kernels.py:288-459, 1749-1875).
+
+    Returns ``(w_hi, w_lo, exp_hi, exp_lo, new_error)``; the reference writes
+    ``new_error`` into ``error`` in place, this restatement returns it.
+    """
+    N, K = weight.shape
+    assert K % bs == 0
+    w = weight.float()
+    wc = w + error if error is not None else w
+    wb = wc.reshape(N, K // bs, bs)
+    e_hi = _block_exponent(wb.abs().amax(dim=-1), FP8_E4M3_MAX)
+    inv_hi = torch.exp2(e_hi).unsqueeze(-1)
+    hi = (wb / inv_hi).clamp(-FP8_E4M3_MAX, FP8_E4M3_MAX).to(E4M3)
+    residual = wb - hi.float() * inv_hi
+    amax_lo = residual.abs().amax(dim=-1)
+    zero = amax_lo < 1e-12
+    e_lo = _block_exponent(amax_lo, FP8_E4M3_MAX)
+    inv_lo = torch.where(zero, torch.ones_like(e_lo), torch.exp2(e_lo)).unsqueeze(-1)
+    lo_in = (residual / inv_lo).clamp(-FP8_E4M3_MAX, FP8_E4M3_MAX)
+    if srr:
+        rand = philox_uniform(seed, offset, N * K).reshape(N, K // bs, bs)
+        lo = _sr_block(lo_in, rand)
+    else:
+        lo = lo_in.to(E4M3)
+    exp_hi = e_hi.to(torch.int8).t().contiguous()
+    exp_lo = torch.where(zero, torch.full_like(e_lo, -128.0), e_lo).to(torch.int8).t().contiguous()
+    hi = hi.reshape(N, K)
+    lo = lo.reshape(N, K)
+    new_error = None
+    if error is not None:
+        # tcfp/kernels.py:1870-1873: from the STORED codes, against the
+        # ORIGINAL weight
+        new_error = w - block_dequantize(hi, exp_hi, bs) - block_dequantize(lo, exp_lo, bs)
+    return hi, lo, exp_hi, exp_lo, new_error
+
+
+# ---------------------------------------------------------------------------
+# GEMMs: FP32 dequantized dual matmuls
+# ---------------------------------------------------------------------------
+
+def dual_gemm_nt(a, inv_a, w_hi, inv_hi, w_lo, inv_lo):
+    """``out = (A.W_hi^T).(s_a s_hi) + (A.W_lo^T).(s_a s_lo)``
+    (tcfp/kernels.py:108-119, 183-184; tcfp/csrc/fused_dual_gemm.h:8)."""
+    af = a.float()
+    out = (af @ w_hi.float().t()) * (inv_a * inv_hi)
+    if w_lo is not None:
+        out = out + (af @ w_lo.float().t()) * (inv_a * inv_lo)
+    return out
+
+
+def dual_gemm_nn(g, inv_g, w_hi, inv_hi, w_lo, inv_lo):
+    """``dX = (g.W_hi).(s_g s_hi) + (g.W_lo).(s_g s_lo)``
+    (tcfp/kernels.py:1604-1666; tcfp/csrc/fused_dual_gemm.h:9)."""
+    gf = g.float()
+    out = (gf @ w_hi.float()) * (inv_g * inv_hi)
+    if w_lo is not None:
+        out = out + (gf @ w_lo.float()) * (inv_g * inv_lo)
+    return out
+
+
+def _deq_lo(codes, exps, bs):
+    # sentinel -128 -> scale 0 (tcfp/kernels.py:762-764)
+    M, K = codes.shape
+    scales = torch.where(exps == -128, torch.zeros((), dtype=torch.float32), torch.exp2(exps.float()))
+    return (codes.float().reshape(M, K // bs, bs) * scales.t().unsqueeze(-1)).reshape(M, K)
+
+
+def block_dual_gemm_nt(a, exp_a, w_hi, exp_hi, w_lo, exp_lo, bs):
+    """Block-scaled forward (tcfp/kernels.py:687-692, 738-778): dequantize,
+    then FP32 matmul -- the comparison the reference's own tests use
+    (tests/test_block_scaling_kernels.py:147-169)."""
+    af = block_dequantize(a, exp_a, bs)
+    out = af @ block_dequantize(w_hi, exp_hi, bs).t()
+    if w_lo is not None:
+        out = out + af @ _deq_lo(w_lo, exp_lo, bs).t()
+    return out
+
+
+def block_backward_dx(g, exp_g, w_hi, exp_hi, w_lo, exp_lo, bs):
+    """Block-scaled dX (tcfp/kernels.py:1146-1189, 2464-2469): g blocks run
+    along D_out, weight blocks along D_in."""
+    gf = block_dequantize(g, exp_g, bs)
+    w = block_dequantize(w_hi, exp_hi, bs)
+    if w_lo is not None:
+        w = w + _deq_lo(w_lo, exp_lo, bs)
+    return gf @ w

@@ -1,0 +1,19 @@
+"""tcfp_b200: the TCFP-12 linear-layer hot path on B200 (sm_100a).
+
+Host side is Python/PyTorch; the compute lives in ``libtcfp_b200.so`` (C ABI in
+``include/tcfp_b200.h``), built in-tree by ``python -m tcfp_b200.build``.
+"""
+from .core import (  # noqa: F401
+    FP8_E4M3_MAX,
+    FP8_E5M2_MAX,
+    ErrorFeedbackState,
+    TCFPMode,
+    absmax,
+    dual_quantize_per_tensor,
+    ensure_column_major,
+    to_fp8_e4m3,
+    to_fp8_e4m3_sr,
+    to_fp8_e5m2,
+)
+
+__version__ = "0.1.0"

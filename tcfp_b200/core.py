@@ -1,0 +1,205 @@
+"""FP8 primitives and error-feedback state with the names and semantics of the
+reference's ``tcfp/core.py``, computed by the CUDA kernels of
+``libtcfp_b200.so``.  CUDA tensors only: there is no CPU implementation here.
+"""
+from __future__ import annotations
+
+from enum import Enum, auto
+
+import torch
+
+from . import _C
+
+# tcfp/core.py:27-43 -- part of the numeric contract
+FP8_E4M3_MAX: float = 448.0
+FP8_E4M3_MIN: float = -448.0
+FP8_E4M3_SMALLEST_NORMAL: float = 2**-6
+FP8_E5M2_MAX: float = 57344.0
+FP8_E5M2_MIN: float = -57344.0
+DEFAULT_BLOCK_SIZE: int = 32
+VALID_BLOCK_SIZES: tuple[int, ...] = (16, 32, 64, 128)
+
+
+class TCFPMode(Enum):
+    """tcfp/core.py:46-49."""
+
+    TCFP12 = auto()
+
+
+def _require_cuda(t: torch.Tensor, who: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{who}: tcfp_b200 runs on CUDA (sm_100) tensors only, got a {t.device} tensor")
+
+
+def _flat2d(t: torch.Tensor) -> tuple[torch.Tensor, int, int]:
+    t = t.contiguous()
+    n = t.numel()
+    if n % 4 != 0:
+        raise RuntimeError(f"tensor size ({n}) must be a multiple of 4 elements")
+    return t, 1, n
+
+
+def _cast(tensor: torch.Tensor, scale: torch.Tensor | None, fp8_dtype: torch.dtype, fmt: int, who: str,
+          stochastic: bool = False, seed: int = 0, offset: int = 0):
+    _require_cuda(tensor, who)
+    src = tensor if tensor.dtype in (torch.float32, torch.bfloat16) else tensor.float()
+    src, R, C = _flat2d(src)
+    out = torch.empty(tensor.shape, device=tensor.device, dtype=fp8_dtype)
+    inv = torch.empty(1, device=tensor.device, dtype=torch.float32)
+    scale_t = None
+    if scale is not None:
+        scale_t = scale.to(device=tensor.device, dtype=torch.float32).reshape(1).contiguous()
+    _C.check(_C.load().tcfp_quantize(
+        _C.ptr(src), _C.dtype_code(src), _C.ptr(out), _C.ptr(inv), None, None, R, C, 0, fmt,
+        None, _C.ptr(scale_t), 1 if stochastic else 0, int(seed), int(offset),
+        _C.ptr(_C.workspace(tensor.device)), _C.stream()))
+    return out, inv
+
+
+def to_fp8_e4m3(tensor: torch.Tensor, scale: torch.Tensor | None = None):
+    """tcfp/core.py:85-106: ``(fp8, inv_scale (1,))`` with
+    ``scale = 448 / max(|t|, 1e-12)`` unless given."""
+    return _cast(tensor, scale, torch.float8_e4m3fn, _C.E4M3, "to_fp8_e4m3")
+
+
+def to_fp8_e5m2(tensor: torch.Tensor, scale: torch.Tensor | None = None):
+    """tcfp/core.py:137-158."""
+    return _cast(tensor, scale, torch.float8_e5m2, _C.E5M2, "to_fp8_e5m2")
+
+
+def absmax(tensor: torch.Tensor, error: torch.Tensor | None = None) -> torch.Tensor:
+    """``max |tensor (+ error)|`` as a 0-dim float32 device tensor
+    (the reduction of tcfp/core.py:100, tcfp/nn/__init__.py:282)."""
+    _require_cuda(tensor, "absmax")
+    src = tensor if tensor.dtype in (torch.float32, torch.bfloat16) else tensor.float()
+    src = src.contiguous()
+    out = torch.empty(1, device=tensor.device, dtype=torch.float32)
+    _C.check(_C.load().tcfp_absmax(_C.ptr(src), _C.dtype_code(src), _C.ptr(error), src.numel(), _C.ptr(out),
+                                   _C.stream()))
+    return out.reshape(())
+
+
+def dual_quantize_per_tensor(weight: torch.Tensor, error: torch.Tensor | None = None, *, srr: bool = False,
+                             update_error: bool = True, seed: int = 0, offset: int = 0,
+                             amax_hi: torch.Tensor | None = None, amax_lo: torch.Tensor | None = None,
+                             want_amax: bool = False):
+    """Steps 1-4 of the reference's per-tensor forward
+    (tcfp/nn/__init__.py:343-383) as fused kernels.
+
+    Returns ``(w_hi, w_lo, inv_hi (1,), inv_lo (1,), amax (2,) | None)``.
+    ``error`` is updated IN PLACE (mode EF) unless ``update_error`` is False.
+    """
+    _require_cuda(weight, "dual_quantize_per_tensor")
+    assert weight.is_contiguous(), "Weight must be contiguous (N, K) row-major"
+    N, K = weight.shape
+    if srr and error is not None:
+        raise ValueError("srr and an error buffer are mutually exclusive")
+    dev = weight.device
+    w_hi = torch.empty((N, K), device=dev, dtype=torch.float8_e4m3fn)
+    w_lo = torch.empty((N, K), device=dev, dtype=torch.float8_e4m3fn)
+    inv_hi = torch.empty(1, device=dev, dtype=torch.float32)
+    inv_lo = torch.empty(1, device=dev, dtype=torch.float32)
+    amax = torch.empty(2, device=dev, dtype=torch.float32) if want_amax else None
+    if srr:
+        mode = _C.Q_SRR
+    elif error is not None:
+        mode = _C.Q_EF if update_error else _C.Q_EF_READONLY
+    else:
+        mode = _C.Q_NONE
+    a_hi = None if amax_hi is None else amax_hi.to(torch.float32).reshape(1).contiguous()
+    a_lo = None if amax_lo is None else amax_lo.to(torch.float32).reshape(1).contiguous()
+    _C.check(_C.load().tcfp_dual_quantize(
+        _C.ptr(weight), _C.dtype_code(weight), _C.ptr(error), _C.ptr(w_hi), _C.ptr(w_lo), _C.ptr(inv_hi),
+        _C.ptr(inv_lo), None, None, N, K, 0, mode, int(seed), int(offset), _C.ptr(a_hi), _C.ptr(a_lo),
+        _C.ptr(amax), _C.ptr(_C.workspace(dev)), _C.stream()))
+    return w_hi, w_lo, inv_hi, inv_lo, amax
+
+
+def to_fp8_e4m3_sr(tensor: torch.Tensor, scale: torch.Tensor | None = None, *, seed: int = 0, offset: int = 0):
+    """tcfp/core.py:109-134 with a seeded Philox stream in place of
+    ``torch.rand_like``: element ``i`` draws ``philox4x32-10(seed, offset + i)``."""
+    return _cast(tensor, scale, torch.float8_e4m3fn, _C.E4M3, "to_fp8_e4m3_sr", stochastic=True, seed=seed,
+                 offset=offset)
+
+
+def ensure_column_major(t: torch.Tensor) -> torch.Tensor:
+    """tcfp/core.py:196-213 (layout helper for ``torch._scaled_mm`` callers)."""
+    assert t.ndim == 2, f"ensure_column_major requires 2-D tensor, got {t.ndim}-D"
+    if t.stride(0) == 1 and t.stride(1) == t.shape[0]:
+        return t
+    return t.t().contiguous().t()
+
+
+class ErrorFeedbackState:
+    """Per-parameter state of the tensor-core path; same five dictionaries,
+    keys and update rules as tcfp/core.py:298-410, so ``ef_state.pt``
+    checkpoints written by either implementation load in the other
+    (tcfp/training/checkpointing.py:200-271)."""
+
+    def __init__(self, ema_decay: float = 0.999, residual_validation_interval: int = 100) -> None:
+        self._buffers: dict[str, torch.Tensor] = {}
+        self._amax_ema: dict[str, torch.Tensor] = {}
+        self._ema_decay: float = ema_decay
+        self._delayed_amax: dict[str, torch.Tensor] = {}
+        self._residual_ratio: dict[str, torch.Tensor] = {}
+        self._step_count: dict[str, int] = {}
+        self._residual_validation_interval: int = residual_validation_interval
+
+    def get_error(self, name: str, like: torch.Tensor) -> torch.Tensor:
+        # tcfp/core.py:320-323
+        if name not in self._buffers or self._buffers[name].shape != like.shape:
+            self._buffers[name] = torch.zeros_like(like, dtype=torch.float32)
+        return self._buffers[name]
+
+    def update_error(self, name: str, error: torch.Tensor) -> None:
+        self._buffers[name] = error.detach()
+
+    def get_amax_ema(self, name: str, current_amax: torch.Tensor) -> torch.Tensor:
+        if name not in self._amax_ema:
+            self._amax_ema[name] = current_amax.detach().clone()
+        else:
+            self._amax_ema[name] = (
+                self._ema_decay * self._amax_ema[name] + (1 - self._ema_decay) * current_amax.detach()
+            )
+        return self._amax_ema[name]
+
+    def get_delayed_amax(self, name: str, current_amax: torch.Tensor) -> torch.Tensor:
+        # tcfp/core.py:341-358: first call returns the current amax unchanged
+        if name not in self._delayed_amax:
+            self._delayed_amax[name] = current_amax.detach().clone()
+            return current_amax
+        prev = self._delayed_amax[name]
+        self._delayed_amax[name] = self._ema_decay * prev + (1 - self._ema_decay) * current_amax.detach()
+        return self._delayed_amax[name]
+
+    def predict_residual_amax(self, name: str, main_amax: torch.Tensor) -> torch.Tensor:
+        # tcfp/core.py:360-372
+        ratio_key = f"{name}.ratio"
+        if ratio_key not in self._residual_ratio:
+            return (main_amax / 8.0).clamp(min=1e-12)
+        return (main_amax * self._residual_ratio[ratio_key]).clamp(min=1e-12)
+
+    def update_residual_ratio(self, name: str, main_amax: torch.Tensor, actual_residual_amax: torch.Tensor) -> None:
+        # tcfp/core.py:374-391
+        ratio = (actual_residual_amax / main_amax.clamp(min=1e-12)).detach()
+        ratio_key = f"{name}.ratio"
+        if ratio_key not in self._residual_ratio:
+            self._residual_ratio[ratio_key] = ratio
+        else:
+            self._residual_ratio[ratio_key] = (
+                self._ema_decay * self._residual_ratio[ratio_key] + (1 - self._ema_decay) * ratio
+            )
+
+    def should_validate_residual(self, name: str) -> bool:
+        # tcfp/core.py:393-403
+        key = f"{name}.steps"
+        count = self._step_count.get(key, 0) + 1
+        self._step_count[key] = count
+        return count == 1 or count % self._residual_validation_interval == 0
+
+    def reset(self) -> None:
+        self._buffers.clear()
+        self._amax_ema.clear()
+        self._delayed_amax.clear()
+        self._residual_ratio.clear()
+        self._step_count.clear()

@@ -1,0 +1,150 @@
+// Shared device helpers for the TCFP-12 hot-path kernels (sm_100a).
+//
+// Everything that decides a quantized byte lives here so that the weight
+// quantizer, the activation/gradient quantizer and the tests agree on one
+// definition.  All float arithmetic that feeds a rounding decision uses the
+// explicit round-to-nearest intrinsics: a contracted FMA would change W_lo
+// and the error buffer relative to the reference's op-by-op torch chain
+// (tcfp/core.py:99-106, tcfp/nn/__init__.py:364-383).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace tcfp {
+
+constexpr float kE4M3Max = 448.0f;     // tcfp/core.py:29
+constexpr float kE5M2Max = 57344.0f;   // tcfp/core.py:35
+constexpr float kAmaxFloor = 1e-12f;   // tcfp/core.py:100, tcfp/kernels.py:251
+
+// ---- FP8 encode / decode ---------------------------------------------------
+template <bool E5M2>
+__device__ __forceinline__ uint8_t encode_fp8(float x) {
+  // round-to-nearest-even with saturation; callers clamp first so saturation
+  // only matters for the deliberately out-of-range probes of the SR search.
+  return (uint8_t)__nv_cvt_float_to_fp8(x, __NV_SATFINITE, E5M2 ? __NV_E5M2 : __NV_E4M3);
+}
+
+template <bool E5M2>
+__device__ __forceinline__ float decode_fp8(uint8_t c) {
+  __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)c, E5M2 ? __NV_E5M2 : __NV_E4M3);
+  return __half2float(__half(h));
+}
+
+__device__ __forceinline__ float clampf(float x, float lim) {
+  return fminf(fmaxf(x, -lim), lim);
+}
+
+// ---- power-of-two block exponent ------------------------------------------
+// e = max(ceil(log2(max(amax,1e-12) / fmax)), -126)   (tcfp/kernels.py:250-256)
+// where log2 is a float32 log2.  q = amax/fmax = 2^k (1+f):
+//   f == 0            -> e = k
+//   f  > 2^-17        -> e = k+1 (log2(1+f) is far above half an ulp of k)
+//   otherwise the float32 result of log2 may round DOWN to k; decide it the
+//   way a correctly rounded float32 log2 does (double log2, then round).
+__device__ __forceinline__ int block_exponent(float amax, float fmax) {
+  amax = fmaxf(amax, kAmaxFloor);
+  float q = __fdiv_rn(amax, fmax);
+  uint32_t b = __float_as_uint(q);
+  int k = (int)((b >> 23) & 0xFF) - 127;
+  uint32_t mant = b & 0x7FFFFFu;
+  int e;
+  if (mant == 0) {
+    e = k;
+  } else if (mant >= 64u) {
+    e = k + 1;
+  } else {
+    float lf = (float)log2((double)q);
+    e = (int)ceilf(lf);
+  }
+  return e < -126 ? -126 : e;
+}
+
+// 2^e as float for e in [-149, 127] (exact, subnormals included)
+__device__ __forceinline__ float exp2_int(int e) {
+  if (e >= -126) return __uint_as_float((uint32_t)(e + 127) << 23);
+  return __uint_as_float(1u << (e + 149));
+}
+
+// ---- Philox4x32-10 ---------------------------------------------------------
+// u = f(first word of philox4x32-10(key = seed, counter = (ctr_lo, ctr_hi, 0, 0)))
+// f: reinterpret as int32, x<0 -> -x-1, times 4.6566127342e-10f.
+// This is the stream tl.rand(seed, offset) produces, which the reference's
+// block quantizer draws at offset n*K + k (tcfp/kernels.py:415-417).
+__device__ __forceinline__ float philox_uniform(uint64_t seed, uint64_t ctr) {
+  uint32_t c0 = (uint32_t)ctr, c1 = (uint32_t)(ctr >> 32), c2 = 0u, c3 = 0u;
+  uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    uint32_t hb = __umulhi(0xCD9E8D57u, c2), lb = 0xCD9E8D57u * c2;
+    uint32_t ha = __umulhi(0xD2511F53u, c0), la = 0xD2511F53u * c0;
+    c0 = hb ^ c1 ^ k0;
+    c2 = ha ^ c3 ^ k1;
+    c1 = lb;
+    c3 = la;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  int32_t x = (int32_t)c0;
+  if (x < 0) x = -x - 1;
+  return __fmul_rn((float)x, 4.6566127342e-10f);
+}
+
+// ---- stochastic rounding, two variants -------------------------------------
+// Variant of the block kernel (tcfp/kernels.py:398-423).  x is already
+// clamped to +-448.
+__device__ __forceinline__ uint8_t sr_block_e4m3(float x, float u) {
+  uint8_t rtn = encode_fp8<false>(x);
+  float rtn_f = decode_fp8<false>(rtn);
+  float diff = __fsub_rn(x, rtn_f);
+  float dir = diff >= 0.f ? 1.f : -1.f;
+  float abs_rtn = fmaxf(fabsf(rtn_f), kAmaxFloor);
+  float nudge = __fmul_rn(__fmul_rn(dir, abs_rtn), 0.25f);
+  uint8_t other = encode_fp8<false>(__fadd_rn(rtn_f, nudge));
+  float other_f = decode_fp8<false>(other);
+  float span = fabsf(__fsub_rn(other_f, rtn_f));
+  float gap = fmaxf(span, 1e-45f);
+  float frac = fminf(__fdiv_rn(fabsf(diff), gap), 1.0f);
+  bool exact = (fabsf(diff) < 1e-45f) || (span < 1e-45f);
+  if (exact) return rtn;
+  return (u < frac) ? other : rtn;
+}
+
+// Variant of the per-tensor path (tcfp/core.py:418-464).
+__device__ __forceinline__ uint8_t sr_tensor_e4m3(float x, float u) {
+  uint8_t lo = encode_fp8<false>(x);
+  float lo_f = decode_fp8<false>(lo);
+  float d = __fsub_rn(x, lo_f);
+  if (x == lo_f) return lo;
+  float dir = d > 0.f ? 1.f : (d < 0.f ? -1.f : 0.f);
+  uint8_t hi = encode_fp8<false>(__fadd_rn(lo_f, __fmul_rn(dir, 0.0078125f)));
+  if (decode_fp8<false>(hi) == lo_f) {
+    float abs_lo = fmaxf(fabsf(lo_f), 0.015625f);
+    float big = __fmul_rn(__fmul_rn(dir, abs_lo), 0.25f);
+    hi = encode_fp8<false>(__fadd_rn(lo_f, big));
+  }
+  float hi_f = decode_fp8<false>(hi);
+  float gap = fmaxf(fabsf(__fsub_rn(hi_f, lo_f)), 1e-45f);
+  float frac = fminf(fmaxf(__fdiv_rn(fabsf(d), gap), 0.f), 1.f);
+  return (u < frac) ? hi : lo;
+}
+
+// ---- packed E8M0 scale-factor layout ---------------------------------------
+// The tensor-core block-scaled MMA takes one E8M0 byte per (row, 32-wide K
+// block).  Scale factors of 128 rows x 4 consecutive scale blocks form one
+// 512-byte chunk: byte (r0*16 + r1*4 + j) for row = 32*r1 + r0 and scale
+// block j.  Chunks are ordered [row_block][k_group].  Exponent e is stored
+// biased (e + 127); the -128 sentinel becomes 0 (2^-127).
+__device__ __forceinline__ uint8_t e8m0_from_exp(int e) {
+  return e <= -127 ? (uint8_t)0 : (uint8_t)(e + 127);
+}
+__host__ __device__ __forceinline__ size_t sf_chunk_offset(int64_t row, int64_t kb, int64_t k_groups) {
+  int64_t rb = row >> 7, r1 = (row >> 5) & 3, r0 = row & 31;
+  int64_t kg = kb >> 2, j = kb & 3;
+  return (size_t)((rb * k_groups + kg) * 512 + r0 * 16 + r1 * 4 + j);
+}
+
+}  // namespace tcfp

@@ -1,0 +1,688 @@
+// K3: fused dual GEMM for sm_100a -- TMA + tcgen05 tensor cores + TMEM.
+//
+//   out(M,N) = A . B_hi (*c_hi)  +  A . B_lo (*c_lo)
+//
+// One CTA owns a 128 x 128 output tile.  The B_hi and B_lo tiles of a K stage
+// sit back to back in shared memory, so ONE tcgen05.mma of shape 128 x 256
+// multiplies the A tile -- staged by TMA once -- against both: accumulator
+// columns [0,128) hold A.B_hi, columns [128,256) hold A.B_lo, and the epilogue
+// combines them.  This is the B200 form of "load the A tile once per K
+// iteration and reuse it for both dot products"
+// (tcfp/kernels.py:117-119, 164-181).
+//
+// Variants (template KIND x B layout):
+//   KIND_F8    kind::f8f6f4, per-tensor FP32 scales applied in the epilogue
+//              (tcfp/kernels.py:74-195, tcfp/csrc/fused_dual_gemm.cu:119-274)
+//   KIND_MXF8  kind::mxf8f6f4.block_scale, E8M0 scale per (row, 32 K) read
+//              from TMEM -- the per-block power-of-two scales of
+//              tcfp/kernels.py:628-796 applied by the tensor core itself
+//   KIND_BF16  kind::f16 on exactly dequantized bf16 operands (block dX,
+//              tcfp/kernels.py:1051-1205)
+//   B K-major  W stored (N,K): forward, out = A.W^T
+//   B MN-major W stored (K,N): backward dX = g.W without a transposed copy
+//
+// Warp roles (192 threads): warp 0 TMA producer, warp 1 MMA issuer and TMEM
+// owner, warps 2-5 epilogue (TMEM -> registers -> swizzled smem -> TMA store).
+// Persistent: grid = min(tiles, SMs), static tile schedule, grouped along M so
+// concurrently running CTAs share A row panels and B column panels in L2.
+//
+// Every wait is bounded: after kWaitLimitNs a role raises the CTA's abort
+// flag, records it in g_device_status and all roles fall through to the
+// common teardown, which still frees TMEM.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "launch.h"
+
+namespace tcfp {
+
+__device__ unsigned int g_device_status = 0;
+
+namespace {
+
+enum { KIND_F8 = 0, KIND_MXF8 = 1, KIND_BF16 = 2 };
+
+constexpr int BM = 128;            // output tile rows
+constexpr int BN = 128;            // output tile columns (per hi / lo half)
+constexpr int kStageRowBytes = 128;  // one swizzle-128B row
+constexpr int kThreads = 192;
+constexpr int kEpiThreads = 128;
+constexpr int kATileBytes = BM * kStageRowBytes;        // 16 KB
+constexpr int kBHalfBytes = BN * kStageRowBytes;        // 16 KB (hi or lo)
+constexpr int kStageBytes = kATileBytes + 2 * kBHalfBytes;  // 48 KB
+constexpr int kSfStageBytes = 3 * 512;                  // SFA, SFB_hi, SFB_lo chunks
+constexpr int kStages = 3;
+constexpr int kGroupM = 16;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+
+struct GemmParams {
+  int M, N, K;
+  int k_stages;        // ceil(K / elements per stage)
+  int has_lo;
+  int a_fmt;           // TCFP_E4M3 / TCFP_E5M2 (FP8 kinds)
+  int block_size;      // MXF8: 32 / 64 / 128
+  const float* s_a;    // F8: per-tensor inverse scales
+  const float* s_hi;
+  const float* s_lo;
+  const float* bias;   // nullable, N floats
+  const uint8_t* sf_a; // MXF8: packed E8M0 chunks
+  const uint8_t* sf_hi;
+  const uint8_t* sf_lo;
+};
+
+// ---------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false when the CTA is aborting.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+#pragma unroll 1
+  for (int i = 0; i < 128; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+#pragma unroll 1
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      *abort_flag = 1;
+      atomicOr(&g_device_status, 1u);
+      return false;
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+               "r"(src), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_cp_sf(uint32_t tmem_addr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(sdesc) : "memory");
+}
+
+template <int KIND>
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accum,
+                                       uint32_t sfa, uint32_t sfb) {
+  if constexpr (KIND == KIND_F8) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum)
+        : "memory");
+  } else if constexpr (KIND == KIND_BF16) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum), "r"(sfa), "r"(sfb)
+        : "memory");
+  }
+}
+
+// 32 lanes x 32 consecutive 32-bit columns -> 32 registers per thread
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xFFFFFFFF;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
+// ---- shared-memory matrix descriptors (SWIZZLE_128B, descriptor version 1) ----
+// bits [0,14) start>>4, [16,30) leading byte offset>>4, [32,46) stride byte
+// offset>>4, [46,48) version, [61,64) swizzle mode (2 = 128B).
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)layout << 61;
+  return d;
+}
+
+// tile id -> (m block, n block): groups of kGroupM row blocks, M fastest inside
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& mb, int& nb) {
+  const int per_group = kGroupM * tiles_n;
+  const int group = tile / per_group;
+  const int first_m = group * kGroupM;
+  const int gm = min(tiles_m - first_m, kGroupM);
+  const int in_group = tile - group * per_group;
+  mb = first_m + in_group % gm;
+  nb = in_group / gm;
+}
+
+template <int KIND>
+struct KindTraits {
+  static constexpr int kElemBytes = (KIND == KIND_BF16) ? 2 : 1;
+  static constexpr int kStageK = kStageRowBytes / kElemBytes;  // K elements per stage
+  static constexpr int kMmaK = 32 / kElemBytes;                // K elements per MMA
+  static constexpr int kAccBufs = (KIND == KIND_MXF8) ? 1 : 2;
+};
+
+template <bool OUT_BF16>
+__host__ __device__ constexpr int staging_bytes() { return OUT_BF16 ? BM * BN * 2 : BM * BN * 4; }
+
+template <int KIND, bool OUT_BF16>
+__host__ __device__ constexpr int smem_bytes() {
+  return 1024 /*alignment slack*/ + kStages * kStageBytes + (KIND == KIND_MXF8 ? kStages * kSfStageBytes : 0) +
+         staging_bytes<OUT_BF16>() + 256 /*barriers*/;
+}
+
+// ---------------------------------------------------------------------------
+// The kernel
+// ---------------------------------------------------------------------------
+template <int KIND, bool B_MN, bool OUT_BF16>
+__global__ void __launch_bounds__(kThreads, 1)
+dual_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_bhi,
+                 const __grid_constant__ CUtensorMap tm_blo, const __grid_constant__ CUtensorMap tm_out,
+                 const GemmParams p) {
+  using T = KindTraits<KIND>;
+  constexpr int kAccBufs = T::kAccBufs;
+  constexpr int kAccCols = 2 * BN;  // hi | lo
+  constexpr uint32_t kTmemCols = 512;
+  constexpr int kSfColBase = kAccBufs * kAccCols;  // MXF8: scale-factor columns follow the accumulator
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* stage_base = smem;
+  uint8_t* staging = stage_base + kStages * kStageBytes;  // 1024-aligned: swizzled TMA store source
+  uint8_t* sf_base = staging + staging_bytes<OUT_BF16>();
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sf_base + (KIND == KIND_MXF8 ? kStages * kSfStageBytes : 0));
+  // bars: full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]
+  const uint32_t bar_full = smem_u32(bars);
+  const uint32_t bar_empty = smem_u32(bars + kStages);
+  const uint32_t bar_tfull = smem_u32(bars + 2 * kStages);
+  const uint32_t bar_tempty = smem_u32(bars + 2 * kStages + 2);
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tiles_m = (p.M + BM - 1) / BM;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_tfull + 8 * b, 1);
+      mbar_init(bar_tempty + 8 * b, kEpiThreads);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0 && lane == 0) {
+    prefetch_tmap(&tm_a);
+    prefetch_tmap(&tm_bhi);
+    prefetch_tmap(&tm_blo);
+    prefetch_tmap(&tm_out);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_holder), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ======================= TMA producer =======================
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      const uint32_t tx_bytes = kATileBytes + (p.has_lo ? 2 : 1) * kBHalfBytes +
+                                (KIND == KIND_MXF8 ? (p.has_lo ? 3 : 2) * 512 : 0);
+      const int k_groups = (KIND == KIND_MXF8) ? ((p.K / p.block_size) + 3) / 4 : 0;
+      bool live = true;
+      for (int tile = blockIdx.x; live && tile < num_tiles; tile += gridDim.x) {
+        int mb, nb;
+        tile_coords(tile, tiles_m, tiles_n, mb, nb);
+        for (int ks = 0; ks < p.k_stages; ++ks) {
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag)) { live = false; break; }
+          const uint32_t full = bar_full + 8 * stage;
+          mbar_expect_tx(full, tx_bytes);
+          const uint32_t sa = smem_u32(stage_base + stage * kStageBytes);
+          const uint32_t sb = sa + kATileBytes;
+          const int k0 = ks * T::kStageK;
+          tma_load_2d(sa, &tm_a, k0, mb * BM, full);
+          if constexpr (!B_MN) {
+            tma_load_2d(sb, &tm_bhi, k0, nb * BN, full);
+            if (p.has_lo) tma_load_2d(sb + kBHalfBytes, &tm_blo, k0, nb * BN, full);
+          } else {
+            // one box per 128-byte-wide column group of the (K, N) weight
+            constexpr int kBoxes = T::kElemBytes;          // 1 (fp8) or 2 (bf16)
+            constexpr int kBoxCols = 128 / T::kElemBytes;  // elements per 128 B
+            constexpr int kBoxBytes = kBHalfBytes / kBoxes;
+#pragma unroll
+            for (int b = 0; b < kBoxes; ++b) {
+              tma_load_2d(sb + b * kBoxBytes, &tm_bhi, nb * BN + b * kBoxCols, k0, full);
+              if (p.has_lo) tma_load_2d(sb + kBHalfBytes + b * kBoxBytes, &tm_blo, nb * BN + b * kBoxCols, k0, full);
+            }
+          }
+          if constexpr (KIND == KIND_MXF8) {
+            const int kg = (ks * (T::kStageK / 32)) / (p.block_size / 32) / 4;
+            const uint32_t ssf = smem_u32(sf_base + stage * kSfStageBytes);
+            bulk_load_1d(ssf, p.sf_a + ((size_t)mb * k_groups + kg) * 512, 512, full);
+            bulk_load_1d(ssf + 512, p.sf_hi + ((size_t)nb * k_groups + kg) * 512, 512, full);
+            if (p.has_lo) bulk_load_1d(ssf + 1024, p.sf_lo + ((size_t)nb * k_groups + kg) * 512, 512, full);
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ======================= MMA issuer =======================
+    if (elect_one()) {
+      const uint32_t n_mma = p.has_lo ? 2 * BN : BN;
+      uint32_t idesc;
+      if constexpr (KIND == KIND_MXF8) {
+        idesc = ((uint32_t)p.a_fmt << 7) | (0u << 10) | ((B_MN ? 1u : 0u) << 16) | ((n_mma >> 3) << 17) | (1u << 23) |
+                ((uint32_t)(BM >> 4) << 24);
+      } else {
+        const uint32_t fa = (KIND == KIND_BF16) ? 1u : (uint32_t)p.a_fmt;
+        const uint32_t fb = (KIND == KIND_BF16) ? 1u : 0u;
+        idesc = (1u << 4) | (fa << 7) | (fb << 10) | ((B_MN ? 1u : 0u) << 16) | ((n_mma >> 3) << 17) |
+                ((uint32_t)(BM >> 4) << 24);
+      }
+      // B descriptor strides
+      constexpr uint32_t kBLbo = B_MN ? (uint32_t)(kBHalfBytes / T::kElemBytes) : 16u;  // MN: bytes between 128 B column groups
+      constexpr uint32_t kBKStep = B_MN ? (uint32_t)(T::kMmaK * kStageRowBytes) : 32u;    // bytes per MMA along K
+      int stage = 0;
+      uint32_t phase = 0;
+      int buf = 0;
+      uint32_t buf_phase = 0;
+      bool live = true;
+      for (int tile = blockIdx.x; live && tile < num_tiles; tile += gridDim.x) {
+        if (!mbar_wait(bar_tempty + 8 * buf, buf_phase ^ 1, abort_flag)) { live = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * kAccCols);
+        for (int ks = 0; ks < p.k_stages; ++ks) {
+          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) { live = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(stage_base + stage * kStageBytes);
+          const uint32_t sb = sa + kATileBytes;
+          uint32_t tsfa = 0, tsfb = 0;
+          int sf_first = 0, sf_shift = 0;
+          if constexpr (KIND == KIND_MXF8) {
+            const uint32_t ssf = smem_u32(sf_base + stage * kSfStageBytes);
+            tsfa = tmem_base + (uint32_t)(kSfColBase + stage * 16);
+            tsfb = tsfa + 4;
+            tc_cp_sf(tsfa, make_desc(ssf, 0, 128, 0));
+            tc_cp_sf(tsfb, make_desc(ssf + 512, 0, 128, 0));
+            if (p.has_lo) tc_cp_sf(tsfb + 4, make_desc(ssf + 1024, 0, 128, 0));
+            // scale byte of MMA j inside this stage: bs 32 -> j, bs 64 -> 2*(ks&1) + j/2, bs 128 -> ks&3
+            if (p.block_size == 32) { sf_first = 0; sf_shift = 0; }
+            else if (p.block_size == 64) { sf_first = 2 * (ks & 1); sf_shift = 1; }
+            else { sf_first = ks & 3; sf_shift = 2; }
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint64_t adesc = make_desc(sa + j * 32, 16, 1024, 2);
+            const uint64_t bdesc = make_desc(sb + j * kBKStep, kBLbo, 1024, 2);
+            uint32_t id = idesc;
+            if constexpr (KIND == KIND_MXF8) {
+              const uint32_t sfid = (uint32_t)(sf_first + (j >> sf_shift));
+              id |= (sfid << 29) | (sfid << 4);
+            }
+            tc_mma<KIND>(d_tmem, adesc, bdesc, id, (ks | j) != 0 ? 1u : 0u, tsfa, tsfb);
+          }
+          tc_commit(bar_empty + 8 * stage);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        if (!live) break;
+        tc_commit(bar_tfull + 8 * buf);
+        if (++buf == kAccBufs) { buf = 0; buf_phase ^= 1; }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ======================= epilogue =======================
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const int r_local = q * 32 + lane;
+    const bool issuer = (threadIdx.x == 64);
+    float c_hi = 1.f, c_lo = 1.f;
+    if constexpr (KIND == KIND_F8) {
+      const float sa = __ldg(p.s_a);
+      c_hi = sa * __ldg(p.s_hi);
+      c_lo = p.has_lo ? sa * __ldg(p.s_lo) : 0.f;
+    }
+    int buf = 0;
+    uint32_t buf_phase = 0;
+    bool live = true;
+    bool stored = false;
+    for (int tile = blockIdx.x; live && tile < num_tiles; tile += gridDim.x) {
+      int mb, nb;
+      tile_coords(tile, tiles_m, tiles_n, mb, nb);
+      if (!mbar_wait(bar_tfull + 8 * buf, buf_phase, abort_flag)) { live = false; break; }
+      tc_fence_after();
+      if (issuer && stored) bulk_wait_read0();  // staging is free again
+      epi_bar_sync();
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * kAccCols);
+#pragma unroll 1
+      for (int g = 0; g < BN / 32; ++g) {
+        uint32_t vh[32], vl[32];
+        tmem_ld32(t_row + g * 32, vh);
+        if (p.has_lo) tmem_ld32(t_row + BN + g * 32, vl);
+        tmem_ld_wait();
+        float o[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float v = __uint_as_float(vh[i]) * c_hi;
+          if (p.has_lo) v = fmaf(__uint_as_float(vl[i]), c_lo, v);
+          o[i] = v;
+        }
+        if (p.bias != nullptr) {
+          const int n0 = nb * BN + g * 32;
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (n0 + i < p.N) o[i] += __ldg(p.bias + n0 + i);
+        }
+        if constexpr (!OUT_BF16) {
+          // piece g: 128 rows x 128 B, 16-byte chunks XOR-swizzled by row
+          uint8_t* piece = staging + g * (BM * 128) + r_local * 128;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            float4 v4 = make_float4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+            *reinterpret_cast<float4*>(piece + ((c ^ (r_local & 7)) << 4)) = v4;
+          }
+        } else {
+          uint8_t* piece = staging + (g >> 1) * (BM * 128) + r_local * 128;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            __nv_bfloat162 b0 = __floats2bfloat162_rn(o[8 * c], o[8 * c + 1]);
+            __nv_bfloat162 b1 = __floats2bfloat162_rn(o[8 * c + 2], o[8 * c + 3]);
+            __nv_bfloat162 b2 = __floats2bfloat162_rn(o[8 * c + 4], o[8 * c + 5]);
+            __nv_bfloat162 b3 = __floats2bfloat162_rn(o[8 * c + 6], o[8 * c + 7]);
+            uint4 v4;
+            v4.x = *reinterpret_cast<uint32_t*>(&b0);
+            v4.y = *reinterpret_cast<uint32_t*>(&b1);
+            v4.z = *reinterpret_cast<uint32_t*>(&b2);
+            v4.w = *reinterpret_cast<uint32_t*>(&b3);
+            const int cc = (g & 1) * 4 + c;
+            *reinterpret_cast<uint4*>(piece + ((cc ^ (r_local & 7)) << 4)) = v4;
+          }
+        }
+      }
+      // accumulator drained: hand the TMEM buffer back to the MMA warp
+      tc_fence_before();
+      mbar_arrive(bar_tempty + 8 * buf);
+      fence_async_smem();
+      epi_bar_sync();
+      if (issuer) {
+        constexpr int kPieces = OUT_BF16 ? BN / 64 : BN / 32;
+        constexpr int kPieceCols = OUT_BF16 ? 64 : 32;
+#pragma unroll
+        for (int pc = 0; pc < kPieces; ++pc) {
+          const int n0 = nb * BN + pc * kPieceCols;
+          if (n0 < p.N) tma_store_2d(&tm_out, smem_u32(staging + pc * (BM * 128)), n0, mb * BM);
+        }
+        bulk_commit();
+        stored = true;
+      }
+      if (++buf == kAccBufs) { buf = 0; buf_phase ^= 1; }
+    }
+    if (issuer && stored) bulk_wait0();
+  }
+
+  // ======================= teardown =======================
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // give copies that are still in flight time to land before the CTA exits
+    for (int i = 0; i < 20; ++i) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// 2-D row-major tensor (rows x cols elements), box = box_cols x box_rows, 128-byte swizzle
+int make_map(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const void* ptr, int64_t rows, int64_t cols,
+             int box_cols, int box_rows) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return fail(TCFP_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15u) || ((cols * elem_bytes) & 15))
+    return fail(TCFP_ERR_INVALID, "GEMM operands need 16-byte aligned base pointers and row pitches");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)(cols * elem_bytes)};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(TCFP_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return TCFP_OK;
+}
+
+template <int KIND, bool B_MN, bool OUT_BF16>
+int launch(const void* a, const void* b_hi, const void* b_lo, void* out, GemmParams p, cudaStream_t stream) {
+  using T = KindTraits<KIND>;
+  const CUtensorMapDataType dt = (KIND == KIND_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  const int eb = T::kElemBytes;
+  CUtensorMap tm_a, tm_bhi, tm_blo, tm_out;
+  int rc;
+  if ((rc = make_map(&tm_a, dt, eb, a, p.M, p.K, T::kStageK, BM)) != TCFP_OK) return rc;
+  if (!B_MN) {
+    if ((rc = make_map(&tm_bhi, dt, eb, b_hi, p.N, p.K, T::kStageK, BN)) != TCFP_OK) return rc;
+    if ((rc = make_map(&tm_blo, dt, eb, b_lo ? b_lo : b_hi, p.N, p.K, T::kStageK, BN)) != TCFP_OK) return rc;
+  } else {
+    if ((rc = make_map(&tm_bhi, dt, eb, b_hi, p.K, p.N, 128 / eb, T::kStageK)) != TCFP_OK) return rc;
+    if ((rc = make_map(&tm_blo, dt, eb, b_lo ? b_lo : b_hi, p.K, p.N, 128 / eb, T::kStageK)) != TCFP_OK) return rc;
+  }
+  if (OUT_BF16)
+    rc = make_map(&tm_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, out, p.M, p.N, 64, BM);
+  else
+    rc = make_map(&tm_out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, out, p.M, p.N, 32, BM);
+  if (rc != TCFP_OK) return rc;
+
+  p.k_stages = (p.K + T::kStageK - 1) / T::kStageK;
+  p.has_lo = b_lo != nullptr;
+  constexpr int smem = smem_bytes<KIND, OUT_BF16>();
+  auto kern = dual_gemm_kernel<KIND, B_MN, OUT_BF16>;
+  static bool configured = false;  // per template instance
+  if (!configured) {
+    CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured = true;
+  }
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kern<<<grid, kThreads, smem, stream>>>(tm_a, tm_bhi, tm_blo, tm_out, p);
+  CUDA_TRY(cudaGetLastError());
+  return TCFP_OK;
+}
+
+int check_dims(const char* who, int64_t M, int64_t N, int64_t K) {
+  if (M <= 0 || N <= 0 || K <= 0 || M > 0x7FFFFFFF || N > 0x7FFFFFFF || K > 0x7FFFFFFF)
+    return fail(TCFP_ERR_INVALID, "%s: bad shape M=%lld N=%lld K=%lld", who, (long long)M, (long long)N, (long long)K);
+  return TCFP_OK;
+}
+
+}  // namespace
+}  // namespace tcfp
+
+using namespace tcfp;
+
+extern "C" int32_t tcfp_check_device_status(void* stream) {
+  CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
+  unsigned int st = 0;
+  CUDA_TRY(cudaMemcpyFromSymbol(&st, g_device_status, sizeof(st)));
+  if (st != 0) {
+    unsigned int zero = 0;
+    CUDA_TRY(cudaMemcpyToSymbol(g_device_status, &zero, sizeof(zero)));
+    return fail(TCFP_ERR_DEVICE, "a kernel gave up a bounded wait (status word 0x%x)", st);
+  }
+  return TCFP_OK;
+}
+
+extern "C" int32_t tcfp_dual_gemm(const uint8_t* a, int32_t a_fmt, const uint8_t* w_hi, const uint8_t* w_lo,
+                                  const float* s_a, const float* s_hi, const float* s_lo, const float* bias, void* out,
+                                  int32_t out_dtype, int64_t M, int64_t N, int64_t K, int32_t trans_b, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (!a || !w_hi || !s_a || !s_hi || !out) return fail(TCFP_ERR_INVALID, "dual_gemm: NULL pointer");
+  if ((w_lo == nullptr) != (s_lo == nullptr)) return fail(TCFP_ERR_INVALID, "dual_gemm: w_lo and s_lo go together");
+  if (a_fmt != TCFP_E4M3 && a_fmt != TCFP_E5M2) return fail(TCFP_ERR_INVALID, "dual_gemm: unknown FP8 format %d", a_fmt);
+  if (out_dtype != TCFP_F32 && out_dtype != TCFP_BF16) return fail(TCFP_ERR_INVALID, "dual_gemm: output must be float32 or bfloat16");
+  int rc = check_dims("dual_gemm", M, N, K);
+  if (rc != TCFP_OK) return rc;
+  GemmParams p{};
+  p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  p.a_fmt = a_fmt;
+  p.s_a = s_a; p.s_hi = s_hi; p.s_lo = s_lo; p.bias = bias;
+  const bool obf = out_dtype == TCFP_BF16;
+  if (!trans_b) return obf ? launch<KIND_F8, false, true>(a, w_hi, w_lo, out, p, stream)
+                           : launch<KIND_F8, false, false>(a, w_hi, w_lo, out, p, stream);
+  return obf ? launch<KIND_F8, true, true>(a, w_hi, w_lo, out, p, stream)
+             : launch<KIND_F8, true, false>(a, w_hi, w_lo, out, p, stream);
+}
+
+extern "C" int32_t tcfp_block_dual_gemm(const uint8_t* a, const uint8_t* sf_a, const uint8_t* w_hi,
+                                        const uint8_t* sf_hi, const uint8_t* w_lo, const uint8_t* sf_lo,
+                                        const float* bias, void* out, int32_t out_dtype, int64_t M, int64_t N,
+                                        int64_t K, int32_t block_size, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (!a || !sf_a || !w_hi || !sf_hi || !out) return fail(TCFP_ERR_INVALID, "block_dual_gemm: NULL pointer");
+  if ((w_lo == nullptr) != (sf_lo == nullptr)) return fail(TCFP_ERR_INVALID, "block_dual_gemm: w_lo and sf_lo go together");
+  if (block_size != 32 && block_size != 64 && block_size != 128)
+    return fail(TCFP_ERR_INVALID, "block_size must be 32, 64, or 128, got %d", block_size);
+  if (out_dtype != TCFP_F32 && out_dtype != TCFP_BF16) return fail(TCFP_ERR_INVALID, "block_dual_gemm: output must be float32 or bfloat16");
+  int rc = check_dims("block_dual_gemm", M, N, K);
+  if (rc != TCFP_OK) return rc;
+  if (K % block_size != 0) return fail(TCFP_ERR_INVALID, "K (%lld) must be divisible by block_size (%d)", (long long)K, block_size);
+  if (((uintptr_t)sf_a | (uintptr_t)sf_hi | (uintptr_t)sf_lo) & 15u)
+    return fail(TCFP_ERR_INVALID, "block_dual_gemm: scale-factor arrays must be 16-byte aligned");
+  GemmParams p{};
+  p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  p.a_fmt = TCFP_E4M3;
+  p.block_size = block_size;
+  p.bias = bias;
+  p.sf_a = sf_a; p.sf_hi = sf_hi; p.sf_lo = sf_lo;
+  return out_dtype == TCFP_BF16 ? launch<KIND_MXF8, false, true>(a, w_hi, w_lo, out, p, stream)
+                                : launch<KIND_MXF8, false, false>(a, w_hi, w_lo, out, p, stream);
+}
+
+extern "C" int32_t tcfp_bf16_dual_gemm(const void* a, const void* b_hi, const void* b_lo, const float* bias, void* out,
+                                       int32_t out_dtype, int64_t M, int64_t N, int64_t K, int32_t trans_b,
+                                       void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (!a || !b_hi || !out) return fail(TCFP_ERR_INVALID, "bf16_dual_gemm: NULL pointer");
+  if (out_dtype != TCFP_F32 && out_dtype != TCFP_BF16) return fail(TCFP_ERR_INVALID, "bf16_dual_gemm: output must be float32 or bfloat16");
+  int rc = check_dims("bf16_dual_gemm", M, N, K);
+  if (rc != TCFP_OK) return rc;
+  GemmParams p{};
+  p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  p.bias = bias;
+  const bool obf = out_dtype == TCFP_BF16;
+  if (!trans_b) return obf ? launch<KIND_BF16, false, true>(a, b_hi, b_lo, out, p, stream)
+                           : launch<KIND_BF16, false, false>(a, b_hi, b_lo, out, p, stream);
+  return obf ? launch<KIND_BF16, true, true>(a, b_hi, b_lo, out, p, stream)
+             : launch<KIND_BF16, true, false>(a, b_hi, b_lo, out, p, stream);
+}

@@ -1,0 +1,146 @@
+"""GPU parity of the tcgen05 dual-GEMM kernels against the FP32 dequantized
+dual matmul of the oracle.  Tolerance: relative Frobenius error <= 1e-3 (the
+FP8 products are exact in FP32; only the accumulation order differs), plus
+the reference's own absolute pins (tests/test_fused_kernels.py:120-134 uses
+atol=rtol=1e-2; tests/test_block_scaling_kernels.py:147-169 uses 1e-3)."""
+import pytest
+import torch
+
+from oracle import tcfp_oracle as O
+from tests.util import acts, rel_fro, weights
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+TOL = 1e-3
+
+SHAPES = [(128, 128, 128), (256, 384, 512), (48, 80, 112), (100, 128, 256), (1024, 1024, 1024), (130, 272, 144)]
+
+
+def _per_tensor_operands(seed, M, N, K, grad=False):
+    x = acts(seed, M, K, torch.float32)
+    w = weights(seed + 1, N, K, std=1.0)
+    a, ia = (O.to_fp8_e5m2 if grad else O.to_fp8_e4m3)(x)
+    hi, lo, ihi, ilo, _, _, _ = O.dual_quantize_per_tensor(w)
+    return a, ia, hi, ihi, lo, ilo
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_dual_gemm_forward(M, N, K):
+    from tcfp_b200.kernels import fused_dual_gemm_forward
+
+    a, ia, hi, ihi, lo, ilo = _per_tensor_operands(100, M, N, K)
+    ref = O.dual_gemm_nt(a, ia, hi, ihi, lo, ilo)
+    out = fused_dual_gemm_forward(a.to(DEV), hi.to(DEV), lo.to(DEV), ia.to(DEV), ihi.to(DEV), ilo.to(DEV))
+    assert out.shape == (M, N) and out.dtype == torch.float32
+    assert rel_fro(out, ref) <= TOL
+    torch.testing.assert_close(out.cpu(), ref, atol=1e-2, rtol=1e-2)
+
+
+def test_dual_gemm_forward_variants():
+    from tcfp_b200.kernels import fused_dual_gemm_forward
+
+    M, N, K = 256, 256, 256
+    a, ia, hi, ihi, lo, ilo = _per_tensor_operands(101, M, N, K)
+    d = lambda t: t.to(DEV)
+    # zero W_lo equals the single GEMM (tests/test_fused_kernels.py:152-176)
+    zero = torch.zeros_like(lo)
+    single = fused_dual_gemm_forward(d(a), d(hi), None, d(ia), d(ihi), None)
+    with_zero = fused_dual_gemm_forward(d(a), d(hi), d(zero), d(ia), d(ihi), d(ilo))
+    torch.testing.assert_close(single, with_zero, atol=1e-4, rtol=1e-4)
+    assert rel_fro(single, O.dual_gemm_nt(a, ia, hi, ihi, None, None)) <= TOL
+    # scale linearity (tests/test_fused_kernels.py:178-204)
+    o1 = fused_dual_gemm_forward(d(a), d(hi), d(lo), d(ia), d(ihi), d(ilo))
+    o2 = fused_dual_gemm_forward(d(a), d(hi), d(lo), d(ia * 2), d(ihi), d(ilo))
+    torch.testing.assert_close(o2, o1 * 2, atol=1e-5, rtol=1e-5)
+    # bias + bf16 output
+    bias = torch.randn(N)
+    ob = fused_dual_gemm_forward(d(a), d(hi), d(lo), d(ia), d(ihi), d(ilo), bias=d(bias), out_dtype=torch.bfloat16)
+    ref = O.dual_gemm_nt(a, ia, hi, ihi, lo, ilo) + bias
+    assert ob.dtype == torch.bfloat16 and rel_fro(ob.float(), ref) <= 5e-3
+    # deterministic run to run
+    assert torch.equal(o1, fused_dual_gemm_forward(d(a), d(hi), d(lo), d(ia), d(ihi), d(ilo)))
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_dual_gemm_backward_dx(M, N, K):
+    """dX = g . W with W in its native (D_out, D_in) layout: here K = D_out is
+    the contraction and N = D_in."""
+    from tcfp_b200.kernels import fused_dual_gemm_backward_dx
+
+    g = acts(200, M, K, torch.float32)
+    w = weights(201, K, N, std=1.0)
+    gq, ig = O.to_fp8_e5m2(g)
+    hi, lo, ihi, ilo, _, _, _ = O.dual_quantize_per_tensor(w)
+    ref = O.dual_gemm_nn(gq, ig, hi, ihi, lo, ilo)
+    out = fused_dual_gemm_backward_dx(gq.to(DEV), hi.to(DEV), lo.to(DEV), ig.to(DEV), ihi.to(DEV), ilo.to(DEV))
+    assert out.shape == (M, N)
+    assert rel_fro(out, ref) <= TOL
+    torch.testing.assert_close(out.cpu(), ref, atol=1e-2, rtol=1e-2)
+
+
+def _block_operands(seed, M, N, K, bs):
+    x = acts(seed, M, K, torch.bfloat16)
+    w = weights(seed + 1, N, K, outliers=True)
+    a, ea = O.block_quantize(x, bs)
+    hi, lo, eh, el, _ = O.dual_quantize_block(w, bs)
+    return a, ea, hi, eh, lo, el
+
+
+@pytest.mark.parametrize("bs", [32, 64, 128])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 384, 512), (100, 100, 256), (512, 640, 1024), (64, 192, 384)])
+def test_block_dual_gemm_forward(M, N, K, bs):
+    from tcfp_b200.kernels import fused_block_scaled_dual_gemm_forward
+
+    a, ea, hi, eh, lo, el = _block_operands(300, M, N, K, bs)
+    ref = O.block_dual_gemm_nt(a, ea, hi, eh, lo, el, bs)
+    d = lambda t: t.to(DEV)
+    out = fused_block_scaled_dual_gemm_forward(d(a), d(hi), d(lo), d(ea), d(eh), d(el), bs)
+    assert rel_fro(out, ref) <= TOL
+    torch.testing.assert_close(out.cpu(), ref, atol=1e-3, rtol=1e-3)
+
+
+def test_block_gemm_single_and_sentinel():
+    from tcfp_b200.kernels import block_scaled_gemm, fused_block_scaled_dual_gemm_forward
+
+    M, N, K, bs = 128, 256, 512, 64
+    a, ea, hi, eh, lo, el = _block_operands(301, M, N, K, bs)
+    d = lambda t: t.to(DEV)
+    single = block_scaled_gemm(d(a), d(hi), d(ea), d(eh), bs)
+    assert rel_fro(single, O.block_dual_gemm_nt(a, ea, hi, eh, None, None, bs)) <= TOL
+    # all-sentinel residual scales -> hi-only result
+    # (tests/test_block_scaling_kernels.py:366-387, compared at atol=1e-2)
+    sent = torch.full_like(el, -128)
+    out = fused_block_scaled_dual_gemm_forward(d(a), d(hi), d(lo), d(ea), d(eh), d(sent), bs)
+    torch.testing.assert_close(out, single, atol=1e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("bs", [32, 64, 128])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 384, 512), (100, 256, 128), (512, 1024, 640)])
+def test_block_backward_dx(M, N, K, bs):
+    """K = D_out (contraction), N = D_in."""
+    from tcfp_b200.kernels import fused_block_scaled_dual_gemm_backward_dx
+
+    g = acts(400, M, K, torch.float32)
+    w = weights(401, K, N, outliers=True)
+    gq, eg = O.block_quantize(g, bs, torch.float8_e5m2)
+    hi, lo, eh, el, _ = O.dual_quantize_block(w, bs)
+    ref = O.block_backward_dx(gq, eg, hi, eh, lo, el, bs)
+    d = lambda t: t.to(DEV)
+    out = fused_block_scaled_dual_gemm_backward_dx(d(gq), d(hi), d(lo), d(eg), d(eh), d(el), bs)
+    assert rel_fro(out, ref) <= TOL
+    torch.testing.assert_close(out.cpu(), ref, atol=1e-2, rtol=1e-2)
+
+
+def test_gemm_rejects_bad_arguments(lib):
+    from tcfp_b200 import _C
+    from tcfp_b200.kernels import fused_dual_gemm_forward
+
+    a = torch.zeros(16, 24, device=DEV, dtype=torch.float8_e4m3fn)   # K = 24: row pitch not 16-byte aligned
+    w = torch.zeros(16, 24, device=DEV, dtype=torch.float8_e4m3fn)
+    s = torch.ones(1, device=DEV)
+    with pytest.raises(RuntimeError, match="16-byte"):
+        fused_dual_gemm_forward(a, w, w, s, s, s)
+    with pytest.raises(AssertionError, match="Shape mismatch"):
+        fused_dual_gemm_forward(a, torch.zeros(16, 32, device=DEV, dtype=torch.float8_e4m3fn), w, s, s, s)
+    assert lib.tcfp_dual_gemm(None, 0, None, None, None, None, None, None, None, 0, 16, 16, 16, 0, None) == -1
+    assert "NULL" in _C.last_error()
