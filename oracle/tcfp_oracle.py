@@ -322,3 +322,103 @@ def block_backward_dx(g, exp_g, w_hi, exp_hi, w_lo, exp_lo, bs):
     if w_lo is not None:
         w = w + _deq_lo(w_lo, exp_lo, bs)
     return gf @ w
+
+
+# ---------------------------------------------------------------------------
+# Layer level: TCFPLinear forward / backward on the tensor-core path
+# ---------------------------------------------------------------------------
+
+class LayerState:
+    """The pieces of ``ErrorFeedbackState`` the per-tensor layer touches
+    (tcfp/core.py:298-410), plus the SRR stream position."""
+
+    def __init__(self, ema_decay: float = 0.999, interval: int = 100):
+        self.error: torch.Tensor | None = None
+        self.delayed_amax: torch.Tensor | None = None
+        self.ratio: torch.Tensor | None = None
+        self.steps = 0
+        self.ema_decay = ema_decay
+        self.interval = interval
+        self.srr_offset = 0
+
+    def get_delayed_amax(self, current):           # tcfp/core.py:341-358
+        if self.delayed_amax is None:
+            self.delayed_amax = current.clone()
+            return current
+        self.delayed_amax = self.ema_decay * self.delayed_amax + (1 - self.ema_decay) * current
+        return self.delayed_amax
+
+    def should_validate(self):                     # tcfp/core.py:393-403
+        self.steps += 1
+        return self.steps == 1 or self.steps % self.interval == 0
+
+    def predict(self, main_amax):                  # tcfp/core.py:360-372
+        if self.ratio is None:
+            return (main_amax / 8.0).clamp(min=1e-12)
+        return (main_amax * self.ratio).clamp(min=1e-12)
+
+    def update_ratio(self, main_amax, actual):     # tcfp/core.py:374-391
+        r = actual / main_amax.clamp(min=1e-12)
+        self.ratio = r if self.ratio is None else self.ema_decay * self.ratio + (1 - self.ema_decay) * r
+
+
+def linear_forward(x, weight, bias, state: LayerState | None, *, srr=False, abd=False, delayed=False,
+                   hp_grad_weight=False, update_ef=True, seed=0):
+    """``_TCFP12TensorCoreFunction.forward`` (tcfp/nn/__init__.py:324-459) with
+    the GEMMs as FP32 dequantized matmuls.  ``state`` is None for SRR / no-EF
+    layers except that SRR uses ``state.srr_offset`` when a state is given.
+    Returns ``(output, ctx)``."""
+    use_ef = state is not None and not srr
+    w = weight.float()
+    if use_ef:
+        if state.error is None or state.error.shape != w.shape:
+            state.error = torch.zeros_like(w)
+        w = w + state.error
+    if delayed and use_ef:
+        current = w.abs().max().clamp(min=1e-12)                       # :282
+        d = state.get_delayed_amax(current)
+        w_hi, inv_hi = to_fp8_e4m3(w, scale=(FP8_E4M3_MAX / d).to(torch.float32))
+        residual = w - w_hi.float() * inv_hi
+        if state.should_validate():                                   # :302-305
+            actual = residual.abs().max().clamp(min=1e-12)
+            state.update_ratio(d, actual)
+            s_lo = (FP8_E4M3_MAX / actual).to(torch.float32)
+        else:
+            s_lo = (FP8_E4M3_MAX / state.predict(d)).to(torch.float32)
+        w_lo, inv_lo = to_fp8_e4m3(residual, scale=s_lo)
+    else:
+        w_hi, inv_hi = to_fp8_e4m3(w)
+        residual = w - w_hi.float() * inv_hi
+        if srr:
+            off = state.srr_offset if state is not None else 0
+            rand = philox_uniform(seed, off, w.numel()).reshape(w.shape)
+            if state is not None:
+                state.srr_offset += w.numel()
+            w_lo, inv_lo = to_fp8_e4m3_sr(residual, rand)
+        else:
+            w_lo, inv_lo = to_fp8_e4m3(residual)
+    if use_ef and update_ef:                                           # :378-383
+        state.error = weight.float() - (w_hi.float() * inv_hi + w_lo.float() * inv_lo)
+    x2d = x.reshape(-1, x.shape[-1])
+    a, inv_a = to_fp8_e4m3(x2d)
+    out = dual_gemm_nt(a, inv_a, w_hi, inv_hi, w_lo, inv_lo)
+    if bias is not None:
+        out = out + bias
+    ctx = dict(x2d=x2d, a=a, inv_a=inv_a, w_hi=w_hi, w_lo=None if abd else w_lo, inv_hi=inv_hi,
+               inv_lo=None if abd else inv_lo, hp=hp_grad_weight, has_bias=bias is not None, shape=x.shape)
+    return out.reshape(*x.shape[:-1], out.shape[-1]), ctx
+
+
+def linear_backward(ctx, grad_out):
+    """``_TCFP12TensorCoreFunction.backward`` (tcfp/nn/__init__.py:461-566)."""
+    g2d = grad_out.reshape(-1, grad_out.shape[-1])
+    gq, inv_g = to_fp8_e5m2(g2d)
+    dx = dual_gemm_nn(gq, inv_g, ctx["w_hi"], ctx["inv_hi"], ctx["w_lo"], ctx["inv_lo"]).reshape(ctx["shape"])
+    if ctx["hp"]:
+        dw = g2d.t() @ ctx["x2d"]
+    elif g2d.shape[0] % 16 != 0:
+        dw = g2d.t() @ (ctx["a"].float() * ctx["inv_a"])
+    else:
+        dw = ((gq.float().t() @ ctx["a"].float()) * (inv_g * ctx["inv_a"]))
+    db = g2d.sum(dim=0) if ctx["has_bias"] else None
+    return dx, dw, db

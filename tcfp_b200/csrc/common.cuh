@@ -124,7 +124,12 @@ __device__ __forceinline__ uint8_t sr_tensor_e4m3(float x, float u) {
   if (decode_fp8<false>(hi) == lo_f) {
     float abs_lo = fmaxf(fabsf(lo_f), 0.015625f);
     float big = __fmul_rn(__fmul_rn(dir, abs_lo), 0.25f);
-    hi = encode_fp8<false>(__fadd_rn(lo_f, big));
+    float probe = __fadd_rn(lo_f, big);
+    // torch's float -> float8_e4m3fn cast does not saturate: anything that
+    // rounds past 448 (|probe| > 464) becomes NaN, every comparison with it
+    // is false and the reference keeps the round-to-nearest code.
+    if (fabsf(probe) > 464.0f) return lo;
+    hi = encode_fp8<false>(probe);
   }
   float hi_f = decode_fp8<false>(hi);
   float gap = fmaxf(fabsf(__fsub_rn(hi_f, lo_f)), 1e-45f);

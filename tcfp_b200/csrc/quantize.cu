@@ -347,8 +347,11 @@ pt_amax_kernel(const void* __restrict__ x, const float* __restrict__ err, int64_
   }
 }
 
+// scale = FP8_MAX / amax as torch evaluates ``python_float / tensor``
+// (tcfp/core.py:100-101): reciprocal of the tensor, then times the scalar --
+// two roundings, not one division.
 __device__ __forceinline__ float pt_scale(float amax, float fmax) {
-  return __fdiv_rn(fmax, fmaxf(amax, kAmaxFloor));  // tcfp/core.py:100-101
+  return __fmul_rn(__frcp_rn(fmaxf(amax, kAmaxFloor)), fmax);
 }
 
 // single-tensor quantize pass (activations / gradients)
@@ -363,7 +366,16 @@ pt_quantize_kernel(const void* __restrict__ x, uint8_t* __restrict__ out, float*
     scale = *scale_in;
   } else {
     const float amax = amax_in ? *amax_in : __uint_as_float(ws[0]);
-    scale = pt_scale(amax, FMAX);
+    if constexpr (X_BF16) {
+      // a bf16 tensor keeps its amax, the clamp, the reciprocal and the
+      // product with FP8_MAX in bf16 (tcfp/core.py:100-101 on a bf16 input);
+      // only the final scale is widened to float32
+      const float a = __bfloat162float(__float2bfloat16_rn(fmaxf(amax, kAmaxFloor)));
+      const float r = __bfloat162float(__float2bfloat16_rn(__frcp_rn(a)));
+      scale = __bfloat162float(__float2bfloat16_rn(__fmul_rn(r, FMAX)));
+    } else {
+      scale = pt_scale(amax, FMAX);
+    }
   }
   if (blockIdx.x == 0 && threadIdx.x == 0) scale_out[0] = __fdiv_rn(1.0f, scale);
   const int64_t nchunks = (nvec + kPtChunk - 1) / kPtChunk;
