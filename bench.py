@@ -114,8 +114,6 @@ def run_reference(args) -> None:
         return
     rows = 2048
     t0 = time.perf_counter()
-    for _ in range(max(args.warmup, 0) and 1):
-        pass
     val, cores, med = _cpu_sample(rows, max(1, min(args.steps, 5)))
     sample = f"first {rows} of 8192 activation rows per step (a {rows}x8192x8192 dual matmul), median of {max(1, min(args.steps, 5))}"
     line = {
