@@ -174,6 +174,18 @@ int32_t tcfp_dual_gemm(const uint8_t* a, int32_t a_fmt,
                        void* stream);
 
 /*
+ * Weight gradient in FP8:  dW(n_out, k_in) = (g^T . x) * (s_g*s_x)  with
+ * g (tokens, n_out) FP8 (E5M2 gradients) and x (tokens, k_in) E4M3, both in
+ * their forward layouts -- the transposes are smem-descriptor bits, not
+ * copies.  Replaces torch._scaled_mm(grad_fp8.t().contiguous(),
+ * ensure_column_major(act_fp8)) at tcfp/nn/__init__.py:546-555.
+ */
+int32_t tcfp_dw_gemm(const uint8_t* g, int32_t g_fmt, const uint8_t* x,
+                     const float* s_g, const float* s_x, void* out,
+                     int32_t out_dtype, int64_t tokens, int64_t n_out,
+                     int64_t k_in, void* stream);
+
+/*
  * Block-scaled forward:
  *   out[m,n] = sum_kb 2^sa[kb,m] * (2^shi[kb,n] * A_kb.Whi_kb + 2^slo[kb,n] * A_kb.Wlo_kb)
  * A (M,K) E4M3, W_* (N,K) E4M3, scale factors as packed E8M0 chunk arrays

@@ -37,6 +37,8 @@ _SIGNATURES = {
                                              c_int32, c_void_p]),
     "tcfp_dual_gemm": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_int32, c_int64, c_int64, c_int64, c_int32, c_void_p]),
+    "tcfp_dw_gemm": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_int64,
+                               c_int64, c_void_p]),
     "tcfp_block_dual_gemm": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                        c_void_p, c_int32, c_int64, c_int64, c_int64, c_int32, c_void_p]),
     "tcfp_bf16_dual_gemm": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_int64,

@@ -256,7 +256,7 @@ __host__ __device__ constexpr int smem_bytes() {
 // ---------------------------------------------------------------------------
 // The kernel
 // ---------------------------------------------------------------------------
-template <int KIND, bool B_MN, bool OUT_BF16>
+template <int KIND, bool B_MN, bool OUT_BF16, bool A_MN = false>
 __global__ void __launch_bounds__(kThreads, 1)
 dual_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_bhi,
                  const __grid_constant__ CUtensorMap tm_blo, const __grid_constant__ CUtensorMap tm_out,
@@ -333,7 +333,16 @@ dual_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           const uint32_t sa = smem_u32(stage_base + stage * kStageBytes);
           const uint32_t sb = sa + kATileBytes;
           const int k0 = ks * T::kStageK;
-          tma_load_2d(sa, &tm_a, k0, mb * BM, full);
+          if constexpr (!A_MN) {
+            tma_load_2d(sa, &tm_a, k0, mb * BM, full);
+          } else {
+            // A given transposed, (K, M) row-major: one box per 128-byte-wide row group
+            constexpr int kABoxes = T::kElemBytes;
+            constexpr int kABoxCols = 128 / T::kElemBytes;
+#pragma unroll
+            for (int b = 0; b < kABoxes; ++b)
+              tma_load_2d(sa + b * (kATileBytes / kABoxes), &tm_a, mb * BM + b * kABoxCols, k0, full);
+          }
           if constexpr (!B_MN) {
             tma_load_2d(sb, &tm_bhi, k0, nb * BN, full);
             if (p.has_lo) tma_load_2d(sb + kBHalfBytes, &tm_blo, k0, nb * BN, full);
@@ -371,9 +380,12 @@ dual_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       } else {
         const uint32_t fa = (KIND == KIND_BF16) ? 1u : (uint32_t)p.a_fmt;
         const uint32_t fb = (KIND == KIND_BF16) ? 1u : 0u;
-        idesc = (1u << 4) | (fa << 7) | (fb << 10) | ((B_MN ? 1u : 0u) << 16) | ((n_mma >> 3) << 17) |
-                ((uint32_t)(BM >> 4) << 24);
+        idesc = (1u << 4) | (fa << 7) | (fb << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
+                ((n_mma >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
       }
+      static_assert(!(A_MN && KIND == KIND_MXF8), "block-scaled kind takes A K-major");
+      constexpr uint32_t kALbo = A_MN ? (uint32_t)(kATileBytes / T::kElemBytes) : 16u;
+      constexpr uint32_t kAKStep = A_MN ? (uint32_t)(T::kMmaK * kStageRowBytes) : 32u;
       // B descriptor strides
       constexpr uint32_t kBLbo = B_MN ? (uint32_t)(kBHalfBytes / T::kElemBytes) : 16u;  // MN: bytes between 128 B column groups
       constexpr uint32_t kBKStep = B_MN ? (uint32_t)(T::kMmaK * kStageRowBytes) : 32u;    // bytes per MMA along K
@@ -407,7 +419,7 @@ dual_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           }
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const uint64_t adesc = make_desc(sa + j * 32, 16, 1024, 2);
+            const uint64_t adesc = make_desc(sa + j * kAKStep, kALbo, 1024, 2);
             const uint64_t bdesc = make_desc(sb + j * kBKStep, kBLbo, 1024, 2);
             uint32_t id = idesc;
             if constexpr (KIND == KIND_MXF8) {
@@ -563,14 +575,16 @@ int make_map(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const voi
   return TCFP_OK;
 }
 
-template <int KIND, bool B_MN, bool OUT_BF16>
+template <int KIND, bool B_MN, bool OUT_BF16, bool A_MN = false>
 int launch(const void* a, const void* b_hi, const void* b_lo, void* out, GemmParams p, cudaStream_t stream) {
   using T = KindTraits<KIND>;
   const CUtensorMapDataType dt = (KIND == KIND_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
   const int eb = T::kElemBytes;
   CUtensorMap tm_a, tm_bhi, tm_blo, tm_out;
   int rc;
-  if ((rc = make_map(&tm_a, dt, eb, a, p.M, p.K, T::kStageK, BM)) != TCFP_OK) return rc;
+  if (!A_MN) rc = make_map(&tm_a, dt, eb, a, p.M, p.K, T::kStageK, BM);
+  else rc = make_map(&tm_a, dt, eb, a, p.K, p.M, 128 / eb, T::kStageK);
+  if (rc != TCFP_OK) return rc;
   if (!B_MN) {
     if ((rc = make_map(&tm_bhi, dt, eb, b_hi, p.N, p.K, T::kStageK, BN)) != TCFP_OK) return rc;
     if ((rc = make_map(&tm_blo, dt, eb, b_lo ? b_lo : b_hi, p.N, p.K, T::kStageK, BN)) != TCFP_OK) return rc;
@@ -587,7 +601,7 @@ int launch(const void* a, const void* b_hi, const void* b_lo, void* out, GemmPar
   p.k_stages = (p.K + T::kStageK - 1) / T::kStageK;
   p.has_lo = b_lo != nullptr;
   constexpr int smem = smem_bytes<KIND, OUT_BF16>();
-  auto kern = dual_gemm_kernel<KIND, B_MN, OUT_BF16>;
+  auto kern = dual_gemm_kernel<KIND, B_MN, OUT_BF16, A_MN>;
   static bool configured = false;  // per template instance
   if (!configured) {
     CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -642,6 +656,23 @@ extern "C" int32_t tcfp_dual_gemm(const uint8_t* a, int32_t a_fmt, const uint8_t
                            : launch<KIND_F8, false, false>(a, w_hi, w_lo, out, p, stream);
   return obf ? launch<KIND_F8, true, true>(a, w_hi, w_lo, out, p, stream)
              : launch<KIND_F8, true, false>(a, w_hi, w_lo, out, p, stream);
+}
+
+extern "C" int32_t tcfp_dw_gemm(const uint8_t* g, int32_t g_fmt, const uint8_t* x, const float* s_g, const float* s_x,
+                                void* out, int32_t out_dtype, int64_t tokens, int64_t n_out, int64_t k_in,
+                                void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (!g || !x || !s_g || !s_x || !out) return fail(TCFP_ERR_INVALID, "dw_gemm: NULL pointer");
+  if (g_fmt != TCFP_E4M3 && g_fmt != TCFP_E5M2) return fail(TCFP_ERR_INVALID, "dw_gemm: unknown FP8 format %d", g_fmt);
+  if (out_dtype != TCFP_F32 && out_dtype != TCFP_BF16) return fail(TCFP_ERR_INVALID, "dw_gemm: output must be float32 or bfloat16");
+  int rc = check_dims("dw_gemm", n_out, k_in, tokens);
+  if (rc != TCFP_OK) return rc;
+  GemmParams p{};
+  p.M = (int)n_out; p.N = (int)k_in; p.K = (int)tokens;
+  p.a_fmt = g_fmt;
+  p.s_a = s_g; p.s_hi = s_x;
+  return out_dtype == TCFP_BF16 ? launch<KIND_F8, true, true, true>(g, x, nullptr, out, p, stream)
+                                : launch<KIND_F8, true, false, true>(g, x, nullptr, out, p, stream);
 }
 
 extern "C" int32_t tcfp_block_dual_gemm(const uint8_t* a, const uint8_t* sf_a, const uint8_t* w_hi,

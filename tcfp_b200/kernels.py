@@ -113,6 +113,21 @@ def fused_dual_gemm_backward_dx(grad_fp8, w_hi_fp8, w_lo_fp8, grad_inv, w_hi_inv
     return out
 
 
+def fp8_weight_grad(grad_fp8, act_fp8, grad_inv, act_inv, *, out_dtype=torch.float32):
+    """``dW = (grad^T @ act) * (s_g * s_a)`` -> ``(D_out, D_in)`` from the
+    gradient ``(M, D_out)`` and the saved activation codes ``(M, D_in)`` as
+    they are (tcfp/nn/__init__.py:546-555 without the transposed copies)."""
+    M, D_out = grad_fp8.shape
+    M2, D_in = act_fp8.shape
+    assert M == M2, f"Shape mismatch: grad({M},{D_out}), act({M2},{D_in})"
+    assert grad_fp8.is_contiguous() and act_fp8.is_contiguous(), "operands must be contiguous"
+    out = torch.empty((D_out, D_in), device=grad_fp8.device, dtype=out_dtype)
+    _C.check(_C.load().tcfp_dw_gemm(
+        _C.ptr(grad_fp8), _fmt(grad_fp8), _C.ptr(act_fp8), _C.ptr(_scalar(grad_inv)), _C.ptr(_scalar(act_inv)),
+        _C.ptr(out), _out_code(out_dtype), M, D_out, D_in, _C.stream()))
+    return out
+
+
 # ---------------------------------------------------------------------------
 # block quantizers (tcfp/kernels.py:1675-1875)
 # ---------------------------------------------------------------------------

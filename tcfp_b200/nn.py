@@ -1,0 +1,397 @@
+"""``TCFPLinear`` on the tensor-core path, with the reference's class name,
+constructor flags, state and autograd behaviour (tcfp/nn/__init__.py:250-1077),
+computed by the sm_100a kernels of ``libtcfp_b200.so``.
+
+Scope: the tensor-core path only (``use_tensor_cores=True``), per-tensor or
+block-32/64/128 scaling, error feedback or stochastic residual rounding,
+delayed scaling, ABD, high-precision weight gradients.  The fake-quantize
+format of the reference (``use_tensor_cores=False``) is a different numeric
+format and is not provided.
+"""
+from __future__ import annotations
+
+import warnings
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import _C
+from .core import (
+    DEFAULT_BLOCK_SIZE,
+    ErrorFeedbackState,
+    TCFPMode,
+    absmax,
+    dual_quantize_per_tensor,
+    to_fp8_e4m3,
+    to_fp8_e5m2,
+)
+from .kernels import (
+    block_dequantize_fp8,
+    block_quantize_fp8,
+    fused_block_scaled_backward_dx,
+    fused_block_scaled_dual_gemm_forward,
+    fused_dual_gemm_backward_dx,
+    fused_dual_gemm_forward,
+    fused_dual_quantize_fp8,
+    fp8_weight_grad,
+)
+
+
+def _flat2d(t: torch.Tensor) -> torch.Tensor:
+    return t.reshape(-1, t.shape[-1]).contiguous()
+
+
+def _master(weight: torch.Tensor) -> torch.Tensor:
+    w = weight.detach()
+    if w.dtype not in (torch.float32, torch.bfloat16):
+        w = w.float()
+    return w.contiguous()
+
+
+# ---------------------------------------------------------------------------
+# per-tensor scaling (tcfp/nn/__init__.py:312-566)
+# ---------------------------------------------------------------------------
+
+class _TCFP12TensorCoreFunction(torch.autograd.Function):
+    """Two FP8 GEMMs sharing one quantized activation, per-tensor scales."""
+
+    @staticmethod
+    def forward(ctx, input, weight, bias, hp_grad_weight, error_state, param_name, delayed_scaling, abd, srr,
+                update_ef, srr_seed, srr_offset):
+        w = _master(weight)
+        error_buf = None
+        if error_state is not None:
+            # lazily zero-initialised FP32 buffer, updated in place by the kernel
+            error_buf = error_state.get_error(param_name, w)
+
+        if delayed_scaling and error_state is not None:
+            # predictive dual-track delayed scaling (tcfp/nn/__init__.py:250-309)
+            current = absmax(w, error_buf).clamp(min=1e-12)
+            delayed = error_state.get_delayed_amax(param_name + ".w_hi", current)
+            if error_state.should_validate_residual(param_name):
+                w_hi, w_lo, inv_hi, inv_lo, amax = dual_quantize_per_tensor(
+                    w, error_buf, update_error=update_ef, amax_hi=delayed, want_amax=True)
+                error_state.update_residual_ratio(param_name, delayed, amax[1].clamp(min=1e-12))
+            else:
+                predicted = error_state.predict_residual_amax(param_name, delayed)
+                w_hi, w_lo, inv_hi, inv_lo, _ = dual_quantize_per_tensor(
+                    w, error_buf, update_error=update_ef, amax_hi=delayed, amax_lo=predicted)
+        else:
+            w_hi, w_lo, inv_hi, inv_lo, _ = dual_quantize_per_tensor(
+                w, error_buf, srr=srr, update_error=update_ef, seed=srr_seed, offset=srr_offset)
+
+        input_shape = input.shape
+        x2d = _flat2d(input)
+        act_fp8, act_inv = to_fp8_e4m3(x2d)                      # always fresh (:390)
+        out2d = fused_dual_gemm_forward(act_fp8, w_hi, w_lo, act_inv, inv_hi, inv_lo,
+                                        bias=None if bias is None else bias.detach().float().contiguous())
+        ctx.hp_grad_weight = hp_grad_weight
+        ctx.input_shape = input_shape
+        ctx.has_bias = bias is not None
+        ctx.abd = abd
+        saved = [x2d if hp_grad_weight else act_fp8, w_hi]
+        if not abd:
+            saved += [w_lo, inv_lo]
+        saved += [inv_hi, act_inv]
+        ctx.save_for_backward(*saved)
+        return out2d.reshape(*input_shape[:-1], out2d.shape[-1])
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        saved = ctx.saved_tensors
+        if ctx.abd:
+            saved_act, w_hi, inv_hi, act_inv = saved
+            w_lo = inv_lo = None
+        else:
+            saved_act, w_hi, w_lo, inv_lo, inv_hi, act_inv = saved
+        g2d = _flat2d(grad_output)
+        if g2d.dtype not in (torch.float32, torch.bfloat16):
+            g2d = g2d.float()
+        grad_fp8, grad_inv = to_fp8_e5m2(g2d)                    # always fresh (:494)
+        grad_input = fused_dual_gemm_backward_dx(grad_fp8, w_hi, w_lo, grad_inv, inv_hi, inv_lo)
+        grad_input = grad_input.reshape(ctx.input_shape)
+        if ctx.hp_grad_weight:
+            grad_weight = g2d.float().t() @ saved_act.float()    # (:541-542)
+        else:
+            grad_weight = fp8_weight_grad(grad_fp8, saved_act, grad_inv, act_inv)   # (:546-555)
+        grad_bias = g2d.float().sum(dim=0) if ctx.has_bias else None
+        return (grad_input, grad_weight, grad_bias) + (None,) * 9
+
+
+# ---------------------------------------------------------------------------
+# block scaling (tcfp/nn/__init__.py:574-761)
+# ---------------------------------------------------------------------------
+
+class _TCFP12BlockScaledFunction(torch.autograd.Function):
+    """Per-block power-of-two scales along K; the tensor core applies them."""
+
+    @staticmethod
+    def forward(ctx, input, weight, bias, scale_block_size, hp_grad_weight, error_state, param_name, abd, srr,
+                update_ef, srr_seed, srr_offset):
+        w = _master(weight)
+        error_buf = None
+        if error_state is not None:
+            error_buf = error_state.get_error(param_name, w)
+        bs = scale_block_size
+        # update_ef False (gradient accumulation, checkpoint recomputation):
+        # the kernel reads the buffer and leaves it alone -- the reference
+        # clones it for the same effect (:607-608)
+        w_hi, w_lo, s_hi, s_lo = fused_dual_quantize_fp8(
+            w, bs, error_buf, srr, seed=srr_seed, offset=srr_offset, update_error=update_ef)
+        input_shape = input.shape
+        x2d = _flat2d(input)
+        if x2d.dtype not in (torch.float32, torch.bfloat16):
+            x2d = x2d.float()
+        act_fp8, act_scales = block_quantize_fp8(x2d, bs, torch.float8_e4m3fn)
+        out2d = fused_block_scaled_dual_gemm_forward(
+            act_fp8, w_hi, w_lo, act_scales, s_hi, s_lo, bs,
+            bias=None if bias is None else bias.detach().float().contiguous())
+        ctx.hp_grad_weight = hp_grad_weight
+        ctx.input_shape = input_shape
+        ctx.has_bias = bias is not None
+        ctx.bs = bs
+        ctx.abd = abd
+        if hp_grad_weight:
+            saved = [x2d, w_hi, s_hi]
+        else:
+            saved = [act_fp8, w_hi, s_hi, act_scales]
+        if not abd:
+            saved += [w_lo, s_lo]
+        ctx.save_for_backward(*saved)
+        return out2d.reshape(*input_shape[:-1], out2d.shape[-1])
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        saved = list(ctx.saved_tensors)
+        bs = ctx.bs
+        if ctx.hp_grad_weight:
+            saved_act, w_hi, s_hi = saved[:3]
+            act_scales = None
+            rest = saved[3:]
+        else:
+            saved_act, w_hi, s_hi, act_scales = saved[:4]
+            rest = saved[4:]
+        w_lo, s_lo = (None, None) if ctx.abd else rest
+        g2d = _flat2d(grad_output)
+        if g2d.dtype not in (torch.float32, torch.bfloat16):
+            g2d = g2d.float()
+        # E5M2 block quantize of the gradient along D_out (:724-726); the same
+        # pass emits the dequantized bf16 copy the dX GEMM consumes
+        grad_fp8, grad_scales, grad_bf16 = block_quantize_fp8(g2d, bs, torch.float8_e5m2, want_bf16=True)
+        grad_input = fused_block_scaled_backward_dx(grad_fp8, w_hi, w_lo, grad_scales, s_hi, s_lo, bs,
+                                                    grad_bf16=grad_bf16).reshape(ctx.input_shape)
+        # dW in full precision, as in the reference (:744-750)
+        if ctx.hp_grad_weight:
+            grad_weight = g2d.float().t() @ saved_act.float()
+        else:
+            grad_weight = g2d.float().t() @ block_dequantize_fp8(saved_act, act_scales, bs)
+        grad_bias = g2d.float().sum(dim=0) if ctx.has_bias else None
+        return (grad_input, grad_weight, grad_bias) + (None,) * 9
+
+
+# ---------------------------------------------------------------------------
+# TCFPLinear (tcfp/nn/__init__.py:769-1077)
+# ---------------------------------------------------------------------------
+
+class TCFPLinear(nn.Module):
+    """Drop-in ``nn.Linear`` on the TCFP-12 tensor-core path.
+
+    Constructor arguments, attribute names, warnings and validation follow
+    tcfp/nn/__init__.py:810-946; flags are re-read on every forward because
+    training policies mutate them live.  ``use_fused_kernel`` and
+    ``use_cuda_ext`` are accepted for compatibility: there is exactly one
+    backend here.  Additional keyword ``srr_seed`` seeds the stochastic
+    residual stream (element ``n*K+k`` of forward call ``i`` draws
+    ``philox(seed, i*N*K + n*K + k)``).
+    """
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = True, mode: TCFPMode = TCFPMode.TCFP12,
+                 block_size: int = DEFAULT_BLOCK_SIZE, *, nf4_residual: bool = False, nf_aware_scaling: bool = False,
+                 sigma_factor: float = 3.0, stochastic_rounding: bool = False, warmup_steps: int = 0,
+                 use_tensor_cores: bool = False, hp_grad_weight: bool = False, error_feedback: bool = True,
+                 delayed_scaling: bool = False, use_fused_kernel: bool = True, use_cuda_ext: bool = True,
+                 scale_block_size: int | None = None, abd: bool = False, srr: bool = False,
+                 srr_seed: int | None = None, device=None, dtype=None) -> None:
+        super().__init__()
+        if nf4_residual and use_tensor_cores and mode == TCFPMode.TCFP12:
+            warnings.warn("nf4_residual is ignored in tensor core mode — NF4 cannot run on tensor cores. "
+                          "The residual uses FP8 E4M3 instead.", stacklevel=2)
+        if delayed_scaling and not use_tensor_cores:
+            warnings.warn("delayed_scaling requires use_tensor_cores=True and is ignored without it.", stacklevel=2)
+        if nf_aware_scaling and use_tensor_cores:
+            raise ValueError("nf_aware_scaling (sigma-based scales) is not provided on the tensor-core path of this build")
+        self.in_features = in_features
+        self.out_features = out_features
+        self.mode = mode
+        self.block_size = block_size
+        self.nf4_residual = nf4_residual
+        self.nf_aware_scaling = nf_aware_scaling
+        self.sigma_factor = sigma_factor
+        self.stochastic_rounding = stochastic_rounding
+        self._warmup_steps = warmup_steps
+        self._warmup_remaining = warmup_steps
+        self.use_tensor_cores = use_tensor_cores
+        self.hp_grad_weight = hp_grad_weight
+        self.use_fused_kernel = use_fused_kernel
+        self.use_cuda_ext = use_cuda_ext
+        if scale_block_size is not None:
+            if scale_block_size not in (32, 64, 128):
+                raise ValueError(f"scale_block_size must be 32, 64, or 128, got {scale_block_size}")
+            if in_features % scale_block_size != 0:
+                raise ValueError(f"in_features ({in_features}) must be divisible by "
+                                 f"scale_block_size ({scale_block_size})")
+            if out_features % scale_block_size != 0:
+                raise ValueError(f"out_features ({out_features}) must be divisible by "
+                                 f"scale_block_size ({scale_block_size}). Backward pass "
+                                 f"block-quantizes gradients along the output dimension.")
+            if not use_tensor_cores:
+                warnings.warn("scale_block_size requires use_tensor_cores=True and is ignored without it.",
+                              stacklevel=2)
+                scale_block_size = None
+            if delayed_scaling and scale_block_size is not None:
+                warnings.warn("Per-block scaling (scale_block_size) and delayed_scaling are mutually exclusive. "
+                              "Ignoring delayed_scaling.", stacklevel=2)
+                delayed_scaling = False
+        self.scale_block_size = scale_block_size
+        self.delayed_scaling = delayed_scaling
+        if abd and not use_tensor_cores:
+            warnings.warn("abd=True requires use_tensor_cores=True and is ignored without it.", stacklevel=2)
+            abd = False
+        self.abd = abd
+        if srr and not use_tensor_cores:
+            warnings.warn("srr=True requires use_tensor_cores=True and is ignored without it.", stacklevel=2)
+            srr = False
+        if srr and delayed_scaling:
+            warnings.warn("srr=True is mutually exclusive with delayed_scaling=True. Disabling delayed_scaling.",
+                          stacklevel=2)
+            delayed_scaling = False
+            self.delayed_scaling = False
+        self.srr = srr
+        self.srr_seed = int(srr_seed if srr_seed is not None else (torch.initial_seed() & 0x7FFFFFFF))
+        self._srr_offset = 0
+
+        self._error_state: ErrorFeedbackState | None = None
+        if use_tensor_cores and error_feedback and not srr:
+            self._error_state = ErrorFeedbackState()
+        self._param_name: str = ""
+        self._last_weight_version: int = -1
+        self._bf16_fallback: bool = False
+
+        kw = {"device": device, "dtype": dtype}
+        self.weight = nn.Parameter(torch.empty(out_features, in_features, **kw))
+        if bias:
+            self.bias = nn.Parameter(torch.empty(out_features, **kw))
+        else:
+            self.register_parameter("bias", None)
+        self.reset_parameters()
+
+    def reset_parameters(self) -> None:
+        nn.init.kaiming_uniform_(self.weight, a=5**0.5)
+        if self.bias is not None:
+            bound = 1 / self.weight.shape[1] ** 0.5
+            nn.init.uniform_(self.bias, -bound, bound)
+
+    def fallback_to_bf16(self) -> None:
+        """Switch this layer to plain ``F.linear`` (tcfp/nn/__init__.py:962-964)."""
+        self._bf16_fallback = True
+
+    def restore_tcfp(self) -> None:
+        self._bf16_fallback = False
+
+    @torch.compiler.disable
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self._bf16_fallback:
+            return F.linear(x, self.weight, self.bias)
+        if self._warmup_remaining > 0:
+            self._warmup_remaining -= 1
+            return F.linear(x, self.weight, self.bias)
+        if not self.use_tensor_cores:
+            raise NotImplementedError(
+                "tcfp_b200 provides the tensor-core path only: construct TCFPLinear with use_tensor_cores=True"
+            )
+        if not x.is_cuda:
+            raise RuntimeError("TCFPLinear (tcfp_b200) runs on CUDA sm_100 devices only; there is no CPU path")
+        _C.load()
+        # skip the EF update when the weight has not changed (gradient
+        # accumulation) or under no_grad (checkpoint recomputation), :989-994
+        ver = self.weight._version
+        update_ef = ver != self._last_weight_version and torch.is_grad_enabled()
+        if update_ef:
+            self._last_weight_version = ver
+        srr = self.srr and self._error_state is None
+        srr_offset = self._srr_offset
+        if srr:
+            self._srr_offset += self.weight.numel()
+        if self.mode == TCFPMode.TCFP12 and self.scale_block_size is not None:
+            return _TCFP12BlockScaledFunction.apply(
+                x, self.weight, self.bias, self.scale_block_size, self.hp_grad_weight, self._error_state,
+                self._param_name, self.abd, srr, update_ef, self.srr_seed, srr_offset)
+        return _TCFP12TensorCoreFunction.apply(
+            x, self.weight, self.bias, self.hp_grad_weight, self._error_state, self._param_name,
+            self.delayed_scaling, self.abd, srr, update_ef, self.srr_seed, srr_offset)
+
+    def extra_repr(self) -> str:
+        parts = [f"in_features={self.in_features}", f"out_features={self.out_features}",
+                 f"bias={self.bias is not None}", f"mode={self.mode.name}", f"block_size={self.block_size}"]
+        if self.use_tensor_cores:
+            parts.append("use_tensor_cores=True")
+        if self.hp_grad_weight:
+            parts.append("hp_grad_weight=True")
+        if self.delayed_scaling:
+            parts.append("delayed_scaling=True")
+        if self.use_fused_kernel:
+            parts.append("use_fused_kernel=True")
+        if self.use_cuda_ext:
+            parts.append("use_cuda_ext=True")
+        if self.scale_block_size is not None:
+            parts.append(f"scale_block_size={self.scale_block_size}")
+        if self.abd:
+            parts.append("abd=True")
+        if self.srr:
+            parts.append("srr=True")
+        if self._warmup_steps > 0:
+            parts.append(f"warmup_steps={self._warmup_steps}")
+        if self._bf16_fallback:
+            parts.append("bf16_fallback=True")
+        return ", ".join(parts)
+
+
+def convert_to_tcfp(model: nn.Module, mode: TCFPMode = TCFPMode.TCFP12, block_size: int = DEFAULT_BLOCK_SIZE, *,
+                    skip_patterns: tuple[str, ...] = ("head",), use_tensor_cores: bool = True,
+                    hp_grad_weight: bool = False, error_feedback: bool = True, delayed_scaling: bool = False,
+                    scale_block_size: int | None = None, abd: bool = False, srr: bool = False,
+                    warmup_steps: int = 0, _prefix: str = "") -> nn.Module:
+    """Swaps every eligible ``nn.Linear`` for a ``TCFPLinear`` sharing the same
+    ``Parameter`` objects (tcfp/nn/__init__.py:1190-1351): names containing a
+    skip pattern are left alone, both dimensions must be multiples of 16 for
+    the tensor-core path, block scaling silently falls back to per-tensor for
+    layers whose dimensions the block size does not divide, and
+    ``_param_name`` becomes the dotted module path (the key of the
+    error-feedback state and of ``ef_state.pt``)."""
+    for name, child in list(model.named_children()):
+        full = f"{_prefix}.{name}" if _prefix else name
+        if any(p in name for p in skip_patterns):
+            continue
+        if isinstance(child, nn.Linear) and not isinstance(child, TCFPLinear):
+            if child.in_features % 16 != 0 or child.out_features % 16 != 0:
+                continue
+            sbs = scale_block_size
+            if sbs is not None and (child.in_features % sbs != 0 or child.out_features % sbs != 0):
+                sbs = None
+            new = TCFPLinear(child.in_features, child.out_features, bias=child.bias is not None, mode=mode,
+                             block_size=block_size, warmup_steps=warmup_steps, use_tensor_cores=use_tensor_cores,
+                             hp_grad_weight=hp_grad_weight, error_feedback=error_feedback,
+                             delayed_scaling=delayed_scaling and sbs is None, scale_block_size=sbs, abd=abd, srr=srr,
+                             device=child.weight.device, dtype=child.weight.dtype)
+            new.weight = child.weight
+            if child.bias is not None:
+                new.bias = child.bias
+            new._param_name = full
+            setattr(model, name, new)
+        else:
+            convert_to_tcfp(child, mode, block_size, skip_patterns=skip_patterns, use_tensor_cores=use_tensor_cores,
+                            hp_grad_weight=hp_grad_weight, error_feedback=error_feedback,
+                            delayed_scaling=delayed_scaling, scale_block_size=scale_block_size, abd=abd, srr=srr,
+                            warmup_steps=warmup_steps, _prefix=full)
+    return model

@@ -1,0 +1,185 @@
+"""GPU: ``TCFPLinear`` against the reference's own recorded outputs (golden
+fixtures made by running the reference on CPU) and against the oracle."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import tcfp_oracle as O
+from tests.golden.cases import LAYER_CASES, layer_inputs
+from tests.util import acts, rel_fro, weights
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+GOLD = np.load(Path(__file__).parent / "golden" / "per_tensor.npz")
+
+
+def f32(a):
+    return torch.from_numpy(a.copy()).view(torch.float32)
+
+
+def i32(t):
+    return t.detach().float().cpu().contiguous().view(torch.int32).numpy()
+
+
+@pytest.mark.parametrize("name", list(LAYER_CASES))
+def test_layer_two_steps_match_reference_golden(name):
+    """Same two SGD steps the generator ran through the reference: EF buffer,
+    delayed amax and residual ratio bit for bit; y, dX, dW, db within 1e-3."""
+    from tcfp_b200.nn import TCFPLinear
+
+    cfg = LAYER_CASES[name]
+    x, w, b, target = layer_inputs(cfg)
+    layer = TCFPLinear(cfg["K"], cfg["N"], bias=cfg["bias"], use_tensor_cores=True, srr=cfg.get("srr", False),
+                       abd=cfg.get("abd", False), delayed_scaling=cfg.get("delayed", False),
+                       hp_grad_weight=cfg.get("hp", False), srr_seed=cfg["seed"]).to(DEV)
+    layer._param_name = "layer"
+    with torch.no_grad():
+        layer.weight.copy_(w)
+        if b is not None:
+            layer.bias.copy_(b)
+    for step in range(2):
+        xin = x.clone().to(DEV).requires_grad_(True)
+        y = layer(xin)
+        assert y.dtype == torch.float32 and y.shape == target.shape
+        loss = ((y - target.to(DEV)) ** 2).mean()
+        layer.zero_grad()
+        loss.backward()
+        pre = f"layer/{name}/step{step}/"
+        pairs = [("y", y), ("dx", xin.grad), ("dw", layer.weight.grad)]
+        if b is not None:
+            pairs.append(("db", layer.bias.grad))
+        for key, val in pairs:
+            ref = f32(GOLD[pre + key]).reshape(val.shape)
+            assert rel_fro(val, ref) <= 1e-3, (key, rel_fro(val, ref))
+        st = layer._error_state
+        if not cfg.get("srr", False):
+            assert np.array_equal(i32(st._buffers["layer"]), GOLD[pre + "ef"]), "EF buffer differs from the reference"
+        else:
+            assert st is None
+        if cfg.get("delayed"):
+            assert np.array_equal(i32(st._delayed_amax["layer.w_hi"].reshape(1)), GOLD[pre + "delayed/layer.w_hi"])
+            assert np.array_equal(i32(st._residual_ratio["layer.ratio"].reshape(1)), GOLD[pre + "ratio/layer.ratio"])
+        with torch.no_grad():
+            # step from the golden gradient so step 2 starts from the reference's weights
+            layer.weight -= 0.05 * f32(GOLD[pre + "dw"]).reshape(layer.weight.shape).to(DEV)
+
+
+@pytest.mark.parametrize("bs", [32, 64, 128])
+@pytest.mark.parametrize("flags", [dict(), dict(abd=True), dict(srr=True), dict(hp_grad_weight=True)])
+def test_block_scaled_layer_against_oracle(bs, flags):
+    from tcfp_b200.nn import TCFPLinear
+
+    M, K, N = 256, 256, 384
+    x = acts(900, M, K, torch.bfloat16)
+    w = weights(901, N, K, outliers=True)
+    b = torch.randn(N, generator=torch.Generator().manual_seed(902)) * 0.1
+    gy = acts(903, M, N, torch.float32)
+    layer = TCFPLinear(K, N, bias=True, use_tensor_cores=True, scale_block_size=bs, srr_seed=77, **flags).to(DEV)
+    layer._param_name = "blk"
+    with torch.no_grad():
+        layer.weight.copy_(w)
+        layer.bias.copy_(b)
+    srr = flags.get("srr", False)
+    err = None if srr else torch.zeros(N, K)
+    for step in range(2):
+        hi, lo, eh, el, new_err = O.dual_quantize_block(w, bs, err, srr=srr, seed=77, offset=step * N * K)
+        a, ea = O.block_quantize(x, bs)
+        y_ref = O.block_dual_gemm_nt(a, ea, hi, eh, lo, el, bs) + b
+        gq, eg = O.block_quantize(gy, bs, torch.float8_e5m2)
+        use_lo = not flags.get("abd", False)
+        dx_ref = O.block_backward_dx(gq, eg, hi, eh, lo if use_lo else None, el if use_lo else None, bs)
+        dw_ref = gy.t() @ (x.float() if flags.get("hp_grad_weight") else O.block_dequantize(a, ea, bs))
+        xin = x.float().to(DEV).requires_grad_(True)   # fp32 leaf: a bf16 leaf would round dX to bf16
+        y = layer(xin)
+        layer.zero_grad()
+        y.backward(gy.to(DEV))
+        assert rel_fro(y, y_ref) <= 1e-3
+        assert rel_fro(xin.grad.float(), dx_ref) <= 1e-3
+        assert rel_fro(layer.weight.grad, dw_ref) <= 1e-3
+        assert rel_fro(layer.bias.grad, gy.sum(0)) <= 1e-5
+        if not srr:
+            assert torch.equal(layer._error_state._buffers["blk"].cpu().view(torch.int32), new_err.view(torch.int32))
+            err = new_err
+        with torch.no_grad():
+            w = w - 0.01 * dw_ref
+            layer.weight.copy_(w)
+
+
+def test_error_feedback_gating():
+    """tests/test_checkpoint_compat.py:32-94, 161-238 of the reference: a
+    repeated forward without an optimizer step, or one under no_grad, must not
+    touch the error buffer."""
+    from tcfp_b200.nn import TCFPLinear
+
+    for kw in (dict(), dict(scale_block_size=64)):
+        layer = TCFPLinear(128, 128, use_tensor_cores=True, **kw).to(DEV)
+        layer._param_name = "g"
+        x = acts(1, 64, 128).to(DEV)
+        layer(x)
+        ef1 = layer._error_state._buffers["g"].clone()
+        assert layer._last_weight_version == layer.weight._version
+        y2 = layer(x)                                   # weight unchanged
+        assert torch.equal(layer._error_state._buffers["g"], ef1)
+        with torch.no_grad():
+            layer.weight.add_(0.01)
+            y3 = layer(x)                               # changed, but under no_grad
+        assert torch.equal(layer._error_state._buffers["g"], ef1)
+        layer(x)                                        # changed and grad enabled
+        assert not torch.equal(layer._error_state._buffers["g"], ef1)
+        assert y2.shape == y3.shape == (64, 128)
+
+
+def test_flag_validation_and_repr():
+    from tcfp_b200.nn import TCFPLinear
+
+    with pytest.warns(UserWarning, match="abd=True requires use_tensor_cores"):
+        TCFPLinear(32, 32, abd=True)
+    with pytest.warns(UserWarning, match="srr=True requires use_tensor_cores"):
+        TCFPLinear(32, 32, srr=True)
+    with pytest.warns(UserWarning, match="mutually exclusive"):
+        layer = TCFPLinear(32, 32, use_tensor_cores=True, srr=True, delayed_scaling=True)
+    assert layer.delayed_scaling is False and layer._error_state is None
+    with pytest.raises(ValueError, match="32, 64, or 128"):
+        TCFPLinear(64, 64, use_tensor_cores=True, scale_block_size=16)
+    with pytest.raises(ValueError, match="in_features.*divisible"):
+        TCFPLinear(48, 64, use_tensor_cores=True, scale_block_size=32)
+    with pytest.raises(ValueError, match="out_features.*divisible"):
+        TCFPLinear(64, 48, use_tensor_cores=True, scale_block_size=32)
+    r = repr(TCFPLinear(64, 64, use_tensor_cores=True, scale_block_size=64, abd=True))
+    assert "scale_block_size=64" in r and "abd=True" in r and "use_tensor_cores=True" in r
+
+
+def test_convert_and_mlp_training_step_loss_decreases():
+    """A 2-layer MLP converted in place trains (tests/test_tcfp12_tensor_cores.py:256-282)."""
+    from tcfp_b200.nn import TCFPLinear, convert_to_tcfp
+
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(torch.nn.Linear(64, 256), torch.nn.GELU(), torch.nn.Linear(256, 64)).to(DEV)
+    convert_to_tcfp(model, skip_patterns=())
+    assert isinstance(model[0], TCFPLinear) and model[0]._param_name == "0" and model[2]._param_name == "2"
+    x = torch.randn(128, 64, device=DEV)
+    target = torch.randn(128, 64, device=DEV)
+    opt = torch.optim.Adam(model.parameters(), lr=1e-2)
+    losses = []
+    for _ in range(50):
+        opt.zero_grad()
+        loss = torch.nn.functional.mse_loss(model(x), target)
+        loss.backward()
+        opt.step()
+        losses.append(loss.item())
+    assert losses[-1] < 0.5 * losses[0]
+
+
+def test_fp8_weight_grad_kernel():
+    from tcfp_b200.kernels import fp8_weight_grad
+
+    for M, N, K in [(128, 128, 128), (200, 256, 384), (1024, 512, 256)]:
+        g = acts(50, M, N, torch.float32)
+        x = acts(51, M, K, torch.float32)
+        gq, ig = O.to_fp8_e5m2(g)
+        xq, ix = O.to_fp8_e4m3(x)
+        ref = (gq.float().t() @ xq.float()) * (ig * ix)
+        out = fp8_weight_grad(gq.to(DEV), xq.to(DEV), ig.to(DEV), ix.to(DEV))
+        assert out.shape == (N, K) and rel_fro(out, ref) <= 1e-3
