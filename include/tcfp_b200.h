@@ -200,6 +200,30 @@ int32_t tcfp_block_dual_gemm(const uint8_t* a, const uint8_t* sf_a,
                              int32_t block_size, void* stream);
 
 /*
+ * No counterpart in the reference.  Same result as tcfp_pack_scales (x3)
+ * followed by tcfp_block_dual_gemm, for callers that hold the scales as
+ * reference-layout int8 exponent planes (K/bs, rows) and cannot allocate the
+ * packed scale-factor buffers: a plugin given only its input and output
+ * buffers, or code on a path where cudaMalloc is off limits.  The packed
+ * scales go into a 6 MiB array built into the library (2 MiB per operand,
+ * tcfp_static_scratch_bytes_per_operand(); every GPU that loads the library
+ * carries it).  Operands whose packed scales exceed 2 MiB (more than
+ * 8192 x 8192 at block 32) are refused with TCFP_ERR_UNSUPPORTED.  This call
+ * allocates nothing.  The first call on each device looks up the array's
+ * device address -- make that call before starting any stream capture.  All
+ * calls on a device share the one array: two calls whose kernels can overlap
+ * on the GPU (different streams) race; serialise them.
+ */
+int32_t tcfp_block_dual_gemm_static(const uint8_t* a, const int8_t* exp_a,
+                                    const uint8_t* w_hi, const int8_t* exp_hi,
+                                    const uint8_t* w_lo, const int8_t* exp_lo,
+                                    const float* bias, void* out,
+                                    int32_t out_dtype, int64_t M, int64_t N,
+                                    int64_t K, int32_t block_size,
+                                    void* stream);
+size_t tcfp_static_scratch_bytes_per_operand(void);
+
+/*
  * BF16 dual GEMM on exactly dequantized operands:
  *   trans_b == 1: out(M,N) = A(M,K) . (B_hi(K,N) + B_lo(K,N))   (block dX)
  *   trans_b == 0: out(M,N) = A(M,K) . (B_hi(N,K) + B_lo(N,K))^T
