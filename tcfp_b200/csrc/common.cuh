@@ -34,6 +34,23 @@ __device__ __forceinline__ float decode_fp8(uint8_t c) {
   return __half2float(__half(h));
 }
 
+// two values per conversion instruction; low byte = first value
+template <bool E5M2>
+__device__ __forceinline__ uint32_t encode_fp8x2(float a, float b) {
+  return (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, E5M2 ? __NV_E5M2 : __NV_E4M3);
+}
+
+// Decode by placing the 7 magnitude bits at the top of a float's exponent /
+// mantissa field and rescaling: exact for normals and subnormals alike
+// (E4M3: bias 7 -> times 2^120; E5M2: bias 15 -> times 2^112).
+template <bool E5M2>
+__device__ __forceinline__ float decode_fp8_fast(uint32_t c) {
+  const uint32_t mag = E5M2 ? ((c & 0x7Fu) << 21) : ((c & 0x7Fu) << 20);
+  const float scale = E5M2 ? 5.192296858534828e33f /* 2^112 */ : 1.329227995784916e36f /* 2^120 */;
+  const float v = __fmul_rn(__uint_as_float(mag), scale);
+  return __uint_as_float(__float_as_uint(v) | ((c & 0x80u) << 24));
+}
+
 __device__ __forceinline__ float clampf(float x, float lim) {
   return fminf(fmaxf(x, -lim), lim);
 }
@@ -45,6 +62,26 @@ __device__ __forceinline__ float clampf(float x, float lim) {
 //   f  > 2^-17        -> e = k+1 (log2(1+f) is far above half an ulp of k)
 //   otherwise the float32 result of log2 may round DOWN to k; decide it the
 //   way a correctly rounded float32 log2 does (double log2, then round).
+// Fast form for fmax = 1.75 * 2^P (448: P = 8, 57344: P = 15).  With
+// amax = 2^a (1+f): f < 0.75 puts amax/fmax strictly between 2^(a-P-1) and
+// 2^(a-P) with a large mantissa, so e = a-P; f >= 0.75 gives a quotient
+// 2^(a-P) * r with r in [1, 1.143), so e = a-P+1 unless r is within a few
+// ulps of 1 -- that sliver goes through the exact rule below.
+__device__ __forceinline__ int block_exponent(float amax, float fmax);
+template <bool E5M2>
+__device__ __forceinline__ int block_exponent_fast(float amax) {
+  constexpr int P = E5M2 ? 15 : 8;
+  amax = fmaxf(amax, kAmaxFloor);
+  const uint32_t b = __float_as_uint(amax);
+  const int a = (int)(b >> 23) - 127;
+  const uint32_t m = b & 0x7FFFFFu;
+  int e;
+  if (m < 0x600000u) e = a - P;
+  else if (m >= 0x600000u + 256u) e = a - P + 1;
+  else return block_exponent(amax, E5M2 ? kE5M2Max : kE4M3Max);
+  return e < -126 ? -126 : e;
+}
+
 __device__ __forceinline__ int block_exponent(float amax, float fmax) {
   amax = fmaxf(amax, kAmaxFloor);
   float q = __fdiv_rn(amax, fmax);

@@ -145,35 +145,40 @@ dual_quantize_block_kernel(const void* __restrict__ w, float* err, uint8_t* __re
 #pragma unroll
       for (int i = 0; i < 4; ++i) wc.v[i] = HAS_ERR ? __fadd_rn(wv[s].v[i], ev[s].v[i]) : wv[s].v[i];
       // --- W_hi
-      const int e_hi = block_exponent(group_max<GROUP>(amax4(wc)), kE4M3Max);
+      const int e_hi = block_exponent_fast<false>(group_max<GROUP>(amax4(wc)));
       const float inv_hi = exp2_int(e_hi), fwd_hi = exp2_int(-e_hi);
-      uint8_t ch[4];
-      f4 res;
+      // the saturating cast makes the reference's clamp to +-448 implicit
+      const uint32_t ph = encode_fp8x2<false>(__fmul_rn(wc.v[0], fwd_hi), __fmul_rn(wc.v[1], fwd_hi)) |
+                          (encode_fp8x2<false>(__fmul_rn(wc.v[2], fwd_hi), __fmul_rn(wc.v[3], fwd_hi)) << 16);
+      f4 hdq, res;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        ch[i] = encode_fp8<false>(clampf(__fmul_rn(wc.v[i], fwd_hi), kE4M3Max));
-        res.v[i] = __fsub_rn(wc.v[i], __fmul_rn(decode_fp8<false>(ch[i]), inv_hi));
+        hdq.v[i] = __fmul_rn(decode_fp8_fast<false>(ph >> (8 * i)), inv_hi);
+        res.v[i] = __fsub_rn(wc.v[i], hdq.v[i]);
       }
       // --- W_lo
       const float amax_lo = group_max<GROUP>(amax4(res));
       const bool zero_res = amax_lo < kAmaxFloor;
-      const int e_lo = block_exponent(amax_lo, kE4M3Max);
+      const int e_lo = block_exponent_fast<false>(amax_lo);
       const float fwd_lo = zero_res ? 1.0f : exp2_int(-e_lo);
-      uint8_t cl[4];
+      uint32_t pl;
+      if constexpr (MODE == TCFP_Q_SRR) {
+        uint8_t cl[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float x = clampf(__fmul_rn(res.v[i], fwd_lo), kE4M3Max);
-        if constexpr (MODE == TCFP_Q_SRR) {
+        for (int i = 0; i < 4; ++i) {
+          float x = clampf(__fmul_rn(res.v[i], fwd_lo), kE4M3Max);
           float u = philox_uniform(seed, offset + (uint64_t)row * (uint64_t)K + (uint64_t)(col + i));
           cl[i] = sr_block_e4m3(x, u);
-        } else {
-          cl[i] = encode_fp8<false>(x);
         }
+        pl = pack4(cl[0], cl[1], cl[2], cl[3]);
+      } else {
+        pl = encode_fp8x2<false>(__fmul_rn(res.v[0], fwd_lo), __fmul_rn(res.v[1], fwd_lo)) |
+             (encode_fp8x2<false>(__fmul_rn(res.v[2], fwd_lo), __fmul_rn(res.v[3], fwd_lo)) << 16);
       }
       if (ok[s]) {
         const size_t idx = (size_t)row * K + col;
-        *reinterpret_cast<uint32_t*>(w_hi + idx) = pack4(ch[0], ch[1], ch[2], ch[3]);
-        *reinterpret_cast<uint32_t*>(w_lo + idx) = pack4(cl[0], cl[1], cl[2], cl[3]);
+        *reinterpret_cast<uint32_t*>(w_hi + idx) = ph;
+        *reinterpret_cast<uint32_t*>(w_lo + idx) = pl;
         if constexpr (MODE == TCFP_Q_EF) {
           // e' = W - deq(hi) - deq(lo), from the stored codes, against the
           // original weight (tcfp/kernels.py:1870-1873).  The sentinel plane
@@ -182,8 +187,8 @@ dual_quantize_block_kernel(const void* __restrict__ w, float* err, uint8_t* __re
           f4 en;
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            float t = __fsub_rn(wv[s].v[i], __fmul_rn(decode_fp8<false>(ch[i]), inv_hi));
-            en.v[i] = __fsub_rn(t, __fmul_rn(decode_fp8<false>(cl[i]), inv_lo));
+            float t = __fsub_rn(wv[s].v[i], hdq.v[i]);
+            en.v[i] = __fsub_rn(t, __fmul_rn(decode_fp8_fast<false>(pl >> (8 * i)), inv_lo));
           }
           store4f(err, idx, en);
         }
@@ -237,19 +242,18 @@ quantize_block_kernel(const void* __restrict__ x, uint8_t* __restrict__ out, int
 #pragma unroll
     for (int s = 0; s < 4; ++s) {
       const int64_t col = col0 + s * 128 + lane * 4;
-      const int e = block_exponent(group_max<GROUP>(amax4(xv[s])), FMAX);
+      const int e = block_exponent_fast<E5M2>(group_max<GROUP>(amax4(xv[s])));
       const float fwd = exp2_int(-e), inv = exp2_int(e);
-      uint8_t c[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) c[i] = encode_fp8<E5M2>(clampf(__fmul_rn(xv[s].v[i], fwd), FMAX));
+      const uint32_t pc = encode_fp8x2<E5M2>(__fmul_rn(xv[s].v[0], fwd), __fmul_rn(xv[s].v[1], fwd)) |
+                          (encode_fp8x2<E5M2>(__fmul_rn(xv[s].v[2], fwd), __fmul_rn(xv[s].v[3], fwd)) << 16);
       if (ok[s]) {
         const size_t idx = (size_t)row * C + col;
-        *reinterpret_cast<uint32_t*>(out + idx) = pack4(c[0], c[1], c[2], c[3]);
+        *reinterpret_cast<uint32_t*>(out + idx) = pc;
         if (deq != nullptr) {
-          __nv_bfloat162 p0 = __floats2bfloat162_rn(__fmul_rn(decode_fp8<E5M2>(c[0]), inv),
-                                                   __fmul_rn(decode_fp8<E5M2>(c[1]), inv));
-          __nv_bfloat162 p1 = __floats2bfloat162_rn(__fmul_rn(decode_fp8<E5M2>(c[2]), inv),
-                                                   __fmul_rn(decode_fp8<E5M2>(c[3]), inv));
+          __nv_bfloat162 p0 = __floats2bfloat162_rn(__fmul_rn(decode_fp8_fast<E5M2>(pc), inv),
+                                                   __fmul_rn(decode_fp8_fast<E5M2>(pc >> 8), inv));
+          __nv_bfloat162 p1 = __floats2bfloat162_rn(__fmul_rn(decode_fp8_fast<E5M2>(pc >> 16), inv),
+                                                   __fmul_rn(decode_fp8_fast<E5M2>(pc >> 24), inv));
           uint2 pk;
           pk.x = *reinterpret_cast<uint32_t*>(&p0);
           pk.y = *reinterpret_cast<uint32_t*>(&p1);
@@ -292,9 +296,8 @@ __global__ void block_dequantize_bf16_kernel(const uint8_t* __restrict__ codes, 
   const int e = (int)exps[(col / BS) * rows + row];
   const float s = (sentinel_zero && e == -128) ? 0.f : exp2_int(e);
   const uint32_t c = *reinterpret_cast<const uint32_t*>(codes + idx);
-  __nv_bfloat162 p0 = __floats2bfloat162_rn(decode_fp8<E5M2>(c & 0xFF) * s, decode_fp8<E5M2>((c >> 8) & 0xFF) * s);
-  __nv_bfloat162 p1 =
-      __floats2bfloat162_rn(decode_fp8<E5M2>((c >> 16) & 0xFF) * s, decode_fp8<E5M2>((c >> 24) & 0xFF) * s);
+  __nv_bfloat162 p0 = __floats2bfloat162_rn(decode_fp8_fast<E5M2>(c) * s, decode_fp8_fast<E5M2>(c >> 8) * s);
+  __nv_bfloat162 p1 = __floats2bfloat162_rn(decode_fp8_fast<E5M2>(c >> 16) * s, decode_fp8_fast<E5M2>(c >> 24) * s);
   uint2 pk;
   pk.x = *reinterpret_cast<uint32_t*>(&p0);
   pk.y = *reinterpret_cast<uint32_t*>(&p1);
@@ -360,7 +363,6 @@ __global__ void __launch_bounds__(kThreads)
 pt_quantize_kernel(const void* __restrict__ x, uint8_t* __restrict__ out, float* __restrict__ scale_out,
                    int64_t nvec, const unsigned int* ws, const float* amax_in, const float* scale_in,
                    uint64_t seed, uint64_t offset) {
-  constexpr float FMAX = E5M2 ? kE5M2Max : kE4M3Max;
   float scale;
   if (scale_in) {
     scale = *scale_in;
@@ -393,14 +395,20 @@ pt_quantize_kernel(const void* __restrict__ x, uint8_t* __restrict__ out, float*
     for (int u = 0; u < kPtUnroll; ++u) {
       if (!ok[u]) continue;
       int64_t v = c * kPtChunk + u * kThreads + threadIdx.x;
-      uint8_t q[4];
+      uint32_t pq;
+      if constexpr (SR && !E5M2) {
+        uint8_t q[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float xs = clampf(__fmul_rn(xv[u].v[i], scale), FMAX);
-        if constexpr (SR && !E5M2) q[i] = sr_tensor_e4m3(xs, philox_uniform(seed, offset + (uint64_t)v * 4u + (uint64_t)i));
-        else q[i] = encode_fp8<E5M2>(xs);
+        for (int i = 0; i < 4; ++i) {
+          const float xs = clampf(__fmul_rn(xv[u].v[i], scale), FMAX);
+          q[i] = sr_tensor_e4m3(xs, philox_uniform(seed, offset + (uint64_t)v * 4u + (uint64_t)i));
+        }
+        pq = pack4(q[0], q[1], q[2], q[3]);
+      } else {
+        pq = encode_fp8x2<E5M2>(__fmul_rn(xv[u].v[0], scale), __fmul_rn(xv[u].v[1], scale)) |
+             (encode_fp8x2<E5M2>(__fmul_rn(xv[u].v[2], scale), __fmul_rn(xv[u].v[3], scale)) << 16);
       }
-      *reinterpret_cast<uint32_t*>(out + (size_t)v * 4) = pack4(q[0], q[1], q[2], q[3]);
+      *reinterpret_cast<uint32_t*>(out + (size_t)v * 4) = pq;
     }
   }
 }
@@ -432,15 +440,17 @@ pt_hi_kernel(const void* __restrict__ w, const float* __restrict__ err, uint8_t*
     for (int u = 0; u < kPtUnroll; ++u) {
       if (!ok[u]) continue;
       int64_t v = c * kPtChunk + u * kThreads + threadIdx.x;
-      uint8_t q[4];
+      f4 wc;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) wc.v[i] = HAS_ERR ? __fadd_rn(xv[u].v[i], ev[u].v[i]) : xv[u].v[i];
+      const uint32_t pq = encode_fp8x2<false>(__fmul_rn(wc.v[0], scale), __fmul_rn(wc.v[1], scale)) |
+                          (encode_fp8x2<false>(__fmul_rn(wc.v[2], scale), __fmul_rn(wc.v[3], scale)) << 16);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        float wc = HAS_ERR ? __fadd_rn(xv[u].v[i], ev[u].v[i]) : xv[u].v[i];
-        q[i] = encode_fp8<false>(clampf(__fmul_rn(wc, scale), kE4M3Max));
-        float r = __fsub_rn(wc, __fmul_rn(decode_fp8<false>(q[i]), inv));
+        float r = __fsub_rn(wc.v[i], __fmul_rn(decode_fp8_fast<false>(pq >> (8 * i)), inv));
         m = fmaxf(m, fabsf(r));
       }
-      *reinterpret_cast<uint32_t*>(w_hi + (size_t)v * 4) = pack4(q[0], q[1], q[2], q[3]);
+      *reinterpret_cast<uint32_t*>(w_hi + (size_t)v * 4) = pq;
     }
   }
   m = group_max<32>(m);
@@ -499,9 +509,9 @@ pt_lo_kernel(const void* __restrict__ w, float* err, uint8_t* w_hi, uint8_t* __r
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         float wc = HAS_ERR ? __fadd_rn(xv[u].v[i], ev[u].v[i]) : xv[u].v[i];
-        if constexpr (FUSED_HI) qh[i] = encode_fp8<false>(clampf(__fmul_rn(wc, sc_hi), kE4M3Max));
+        if constexpr (FUSED_HI) qh[i] = encode_fp8<false>(__fmul_rn(wc, sc_hi));
         else qh[i] = (uint8_t)(hv[u] >> (8 * i));
-        float hdeq = __fmul_rn(decode_fp8<false>(qh[i]), inv_hi);
+        float hdeq = __fmul_rn(decode_fp8_fast<false>(qh[i]), inv_hi);
         float r = __fsub_rn(wc, hdeq);
         if constexpr (FUSED_HI) m = fmaxf(m, fabsf(r));
         float xs = clampf(__fmul_rn(r, sc_lo), kE4M3Max);
@@ -512,7 +522,7 @@ pt_lo_kernel(const void* __restrict__ w, float* err, uint8_t* w_hi, uint8_t* __r
         }
         if constexpr (MODE == TCFP_Q_EF) {
           // tcfp/nn/__init__.py:379-382: W - (hi*inv_hi + lo*inv_lo)
-          float recon = __fadd_rn(hdeq, __fmul_rn(decode_fp8<false>(ql[i]), inv_lo));
+          float recon = __fadd_rn(hdeq, __fmul_rn(decode_fp8_fast<false>(ql[i]), inv_lo));
           en.v[i] = __fsub_rn(xv[u].v[i], recon);
         }
       }
