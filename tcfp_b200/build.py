@@ -23,6 +23,7 @@ COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC"]
 UNITS = [
     ("quantize.cu", ["--fmad=false"]),
     ("gemm_sm100.cu", []),
+    ("gemm2_sm100.cu", []),
     ("noalloc.cu", []),
     ("api.cu", []),
 ]

@@ -30,17 +30,29 @@
 // flag, records it in g_device_status and all roles fall through to the
 // common teardown, which still frees TMEM.
 #include <cuda.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "launch.h"
+#include "sm100_ptx.cuh"
 
 namespace tcfp {
 
 __device__ unsigned int g_device_status = 0;
 
-namespace {
+unsigned int* device_status_ptr() {
+  static unsigned int* cached[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!cached[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_device_status) != cudaSuccess) return nullptr;
+    cached[dev] = static_cast<unsigned int*>(p);
+  }
+  return cached[dev];
+}
 
-enum { KIND_F8 = 0, KIND_MXF8 = 1, KIND_BF16 = 2 };
+namespace {
 
 constexpr int BM = 128;            // output tile rows
 constexpr int BN = 128;            // output tile columns (per hi / lo half)
@@ -53,7 +65,6 @@ constexpr int kStageBytes = kATileBytes + 2 * kBHalfBytes;  // 48 KB
 constexpr int kSfStageBytes = 3 * 512;                  // SFA, SFB_hi, SFB_lo chunks
 constexpr int kStages = 3;
 constexpr int kGroupM = 16;
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 
 struct GemmParams {
   int M, N, K;
@@ -68,162 +79,8 @@ struct GemmParams {
   const uint8_t* sf_a; // MXF8: packed E8M0 chunks
   const uint8_t* sf_hi;
   const uint8_t* sf_lo;
+  unsigned int* status;  // device status word
 };
-
-// ---------------------------------------------------------------------------
-// PTX wrappers
-// ---------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ unsigned long long globaltimer_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait.  Returns false when the CTA is aborting.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-#pragma unroll 1
-  for (int i = 0; i < 128; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = globaltimer_ns();
-#pragma unroll 1
-  while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (globaltimer_ns() - t0 > kWaitLimitNs) {
-      *abort_flag = 1;
-      atomicOr(&g_device_status, 1u);
-      return false;
-    }
-  }
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-               "l"(src), "r"(bytes), "r"(bar)
-               : "memory");
-}
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int c0, int c1) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
-               "r"(src), "r"(c0), "r"(c1)
-               : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
-  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_cp_sf(uint32_t tmem_addr, uint64_t sdesc) {
-  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(sdesc) : "memory");
-}
-
-template <int KIND>
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accum,
-                                       uint32_t sfa, uint32_t sfb) {
-  if constexpr (KIND == KIND_F8) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum)
-        : "memory");
-  } else if constexpr (KIND == KIND_BF16) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum)
-        : "memory");
-  } else {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(d_tmem),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum), "r"(sfa), "r"(sfb)
-        : "memory");
-  }
-}
-
-// 32 lanes x 32 consecutive 32-bit columns -> 32 registers per thread
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "elect.sync _|p, 0xFFFFFFFF;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(pred));
-  return pred != 0;
-}
-
-// ---- shared-memory matrix descriptors (SWIZZLE_128B, descriptor version 1) ----
-// bits [0,14) start>>4, [16,30) leading byte offset>>4, [32,46) stride byte
-// offset>>4, [46,48) version, [61,64) swizzle mode (2 = 128B).
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr >> 4) & 0x3FFF);
-  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
-  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)layout << 61;
-  return d;
-}
 
 // tile id -> (m block, n block): groups of kGroupM row blocks, M fastest inside
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& mb, int& nb) {
@@ -327,7 +184,7 @@ dual_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         int mb, nb;
         tile_coords(tile, tiles_m, tiles_n, mb, nb);
         for (int ks = 0; ks < p.k_stages; ++ks) {
-          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag)) { live = false; break; }
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status)) { live = false; break; }
           const uint32_t full = bar_full + 8 * stage;
           mbar_expect_tx(full, tx_bytes);
           const uint32_t sa = smem_u32(stage_base + stage * kStageBytes);
@@ -395,11 +252,11 @@ dual_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       uint32_t buf_phase = 0;
       bool live = true;
       for (int tile = blockIdx.x; live && tile < num_tiles; tile += gridDim.x) {
-        if (!mbar_wait(bar_tempty + 8 * buf, buf_phase ^ 1, abort_flag)) { live = false; break; }
+        if (!mbar_wait(bar_tempty + 8 * buf, buf_phase ^ 1, abort_flag, p.status)) { live = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * kAccCols);
         for (int ks = 0; ks < p.k_stages; ++ks) {
-          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) { live = false; break; }
+          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status)) { live = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(stage_base + stage * kStageBytes);
           const uint32_t sb = sa + kATileBytes;
@@ -455,7 +312,7 @@ dual_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     for (int tile = blockIdx.x; live && tile < num_tiles; tile += gridDim.x) {
       int mb, nb;
       tile_coords(tile, tiles_m, tiles_n, mb, nb);
-      if (!mbar_wait(bar_tfull + 8 * buf, buf_phase, abort_flag)) { live = false; break; }
+      if (!mbar_wait(bar_tfull + 8 * buf, buf_phase, abort_flag, p.status)) { live = false; break; }
       tc_fence_after();
       if (issuer && stored) bulk_wait_read0();  // staging is free again
       epi_bar_sync();
@@ -598,6 +455,7 @@ int launch(const void* a, const void* b_hi, const void* b_lo, void* out, GemmPar
     rc = make_map(&tm_out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, out, p.M, p.N, 32, BM);
   if (rc != TCFP_OK) return rc;
 
+  p.status = device_status_ptr();
   p.k_stages = (p.K + T::kStageK - 1) / T::kStageK;
   p.has_lo = b_lo != nullptr;
   constexpr int smem = smem_bytes<KIND, OUT_BF16>();
@@ -612,6 +470,17 @@ int launch(const void* a, const void* b_hi, const void* b_lo, void* out, GemmPar
   kern<<<grid, kThreads, smem, stream>>>(tm_a, tm_bhi, tm_blo, tm_out, p);
   CUDA_TRY(cudaGetLastError());
   return TCFP_OK;
+}
+
+// The pair kernel needs at least one full 256-row tile to pay off; TCFP_GEMM_ONE_SM=1
+// forces the one-SM kernel (used by tests to cover both).
+bool use_pair_kernel(int64_t M) {
+  static int forced = -1;
+  if (forced < 0) {
+    const char* e = getenv("TCFP_GEMM_ONE_SM");
+    forced = (e && e[0] == '1') ? 1 : 0;
+  }
+  return forced == 0 && M >= 256;
 }
 
 int check_dims(const char* who, int64_t M, int64_t N, int64_t K) {
@@ -652,6 +521,9 @@ extern "C" int32_t tcfp_dual_gemm(const uint8_t* a, int32_t a_fmt, const uint8_t
   p.a_fmt = a_fmt;
   p.s_a = s_a; p.s_hi = s_hi; p.s_lo = s_lo; p.bias = bias;
   const bool obf = out_dtype == TCFP_BF16;
+  if (use_pair_kernel(M))
+    return pair_gemm_dispatch(KIND_F8, trans_b != 0, obf, a, w_hi, w_lo, nullptr, nullptr, nullptr, out, (int)M, (int)N,
+                              (int)K, a_fmt, 0, s_a, s_hi, s_lo, bias, stream);
   if (!trans_b) return obf ? launch<KIND_F8, false, true>(a, w_hi, w_lo, out, p, stream)
                            : launch<KIND_F8, false, false>(a, w_hi, w_lo, out, p, stream);
   return obf ? launch<KIND_F8, true, true>(a, w_hi, w_lo, out, p, stream)
@@ -696,6 +568,9 @@ extern "C" int32_t tcfp_block_dual_gemm(const uint8_t* a, const uint8_t* sf_a, c
   p.block_size = block_size;
   p.bias = bias;
   p.sf_a = sf_a; p.sf_hi = sf_hi; p.sf_lo = sf_lo;
+  if (use_pair_kernel(M))
+    return pair_gemm_dispatch(KIND_MXF8, false, out_dtype == TCFP_BF16, a, w_hi, w_lo, sf_a, sf_hi, sf_lo, out, (int)M,
+                              (int)N, (int)K, TCFP_E4M3, block_size, nullptr, nullptr, nullptr, bias, stream);
   return out_dtype == TCFP_BF16 ? launch<KIND_MXF8, false, true>(a, w_hi, w_lo, out, p, stream)
                                 : launch<KIND_MXF8, false, false>(a, w_hi, w_lo, out, p, stream);
 }
@@ -712,6 +587,9 @@ extern "C" int32_t tcfp_bf16_dual_gemm(const void* a, const void* b_hi, const vo
   p.M = (int)M; p.N = (int)N; p.K = (int)K;
   p.bias = bias;
   const bool obf = out_dtype == TCFP_BF16;
+  if (use_pair_kernel(M))
+    return pair_gemm_dispatch(KIND_BF16, trans_b != 0, obf, a, b_hi, b_lo, nullptr, nullptr, nullptr, out, (int)M, (int)N,
+                              (int)K, 0, 0, nullptr, nullptr, nullptr, bias, stream);
   if (!trans_b) return obf ? launch<KIND_BF16, false, true>(a, b_hi, b_lo, out, p, stream)
                            : launch<KIND_BF16, false, false>(a, b_hi, b_lo, out, p, stream);
   return obf ? launch<KIND_BF16, true, true>(a, b_hi, b_lo, out, p, stream)

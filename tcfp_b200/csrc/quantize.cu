@@ -214,7 +214,6 @@ quantize_block_kernel(const void* __restrict__ x, uint8_t* __restrict__ out, int
                       uint8_t* __restrict__ sf, __nv_bfloat16* __restrict__ deq, int64_t R, int64_t C) {
   constexpr int GROUP = BS / 4;
   constexpr int kBlocksPerTile = kTileCols / BS;
-  constexpr float FMAX = E5M2 ? kE5M2Max : kE4M3Max;
   __shared__ int8_t s_e[kBlocksPerTile][kTileRows];
 
   const int64_t tiles_c = (C + kTileCols - 1) / kTileCols;
@@ -363,6 +362,7 @@ __global__ void __launch_bounds__(kThreads)
 pt_quantize_kernel(const void* __restrict__ x, uint8_t* __restrict__ out, float* __restrict__ scale_out,
                    int64_t nvec, const unsigned int* ws, const float* amax_in, const float* scale_in,
                    uint64_t seed, uint64_t offset) {
+  constexpr float FMAX = E5M2 ? kE5M2Max : kE4M3Max;
   float scale;
   if (scale_in) {
     scale = *scale_in;
