@@ -43,28 +43,43 @@ def _peaks() -> dict:
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
-
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clock and throttle reasons through NVML (read-only) in a
+    background thread while the timed region runs."""
 
     def __init__(self, index: int):
         self.index = index
-        self.samples: list[list[str]] = []
+        self.sm: list[int] = []
+        self.reasons_seen = 0
+        self.sm_max = None
         self._stop = threading.Event()
         self._thread = threading.Thread(target=self._run, daemon=True)
+        self._nv = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.sm_max = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._nv = None
 
     def _run(self):
+        nv = self._nv
         while not self._stop.is_set():
             try:
-                out = subprocess.run(
-                    ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-i", str(self.index)],
-                    capture_output=True, text=True, timeout=5).stdout.strip()
-                if out:
-                    self.samples.append([c.strip() for c in out.splitlines()[0].split(",")])
+                if nv is not None:
+                    self.sm.append(int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                    self.reasons_seen |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._h))
+                else:
+                    out = subprocess.run(["nvidia-smi", "--query-gpu=clocks.sm,clocks.max.sm", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout
+                    a, b = (int(v) for v in out.strip().splitlines()[0].split(","))
+                    self.sm.append(a)
+                    self.sm_max = b
             except Exception:
                 pass
-            self._stop.wait(0.05)
+            self._stop.wait(0.002)
 
     def __enter__(self):
         self._thread.start()
@@ -75,12 +90,11 @@ class ClockSampler:
         self._thread.join(timeout=6)
 
     def summary(self) -> dict:
-        sm = sorted(int(s[0]) for s in self.samples if s and s[0].isdigit())
-        mx = [int(s[1]) for s in self.samples if len(s) > 1 and s[1].isdigit()]
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(len(s) > 2 + i and s[2 + i].lower().startswith("active") for s in self.samples)]
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(self.samples)}
+        sm = sorted(self.sm)
+        names = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+        reasons = [n for bit, n in names.items() if self.reasons_seen & bit]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": self.sm_max, "reasons": reasons,
+                "samples": len(sm)}
 
 
 def _cpu_sample(rows: int, passes: int):
@@ -106,6 +120,42 @@ def _cpu_sample(rows: int, passes: int):
     times.sort()
     med = times[len(times) // 2]
     return 4.0 * rows * N * K / med / 1e12, cores, med
+
+
+def _mlp_train_step_ms(world: int, dev, timed_fn) -> dict:
+    """BASELINE.json configs[0] on the GPU path: MLP 1024->4096->1024 (GELU),
+    8192 tokens bf16, per-tensor scaling with error feedback, Adam; one step =
+    zero_grad / forward / MSE / backward / optimizer step.  With N > 1 the MLP
+    is tensor-parallel (column-parallel up, row-parallel down, one NCCL
+    all-reduce forward and one backward)."""
+    import torch
+
+    from tcfp_b200.nn import TCFPLinear
+    from tcfp_b200.tp import ParallelMLP
+
+    d, h, tokens = 1024, 4096, 8192
+    g = torch.Generator().manual_seed(1001)
+    x = torch.randn(tokens, d, generator=g).to(torch.bfloat16).to(dev)
+    target = torch.randn(tokens, d, generator=g).to(dev)
+    torch.manual_seed(1001)
+    if world > 1:
+        model = ParallelMLP(d, h).to(dev)
+    else:
+        model = torch.nn.Sequential(TCFPLinear(d, h, use_tensor_cores=True), torch.nn.GELU(),
+                                    TCFPLinear(h, d, use_tensor_cores=True)).to(dev)
+        model[0]._param_name, model[2]._param_name = "fc1", "fc2"
+    opt = torch.optim.Adam(model.parameters(), lr=1e-4)
+
+    def step():
+        opt.zero_grad(set_to_none=True)
+        loss = torch.nn.functional.mse_loss(model(x), target)
+        loss.backward()
+        opt.step()
+
+    steps = 10
+    ms = timed_fn(step, steps, 3) / steps
+    return {"config": "MLP 1024->4096->1024 GELU, 8192 tokens bf16, per-tensor EF, Adam, fwd+bwd+step",
+            "ms_per_step": ms, "parallelism": f"tp{world}" if world > 1 else "single GPU"}
 
 
 def run_reference(args) -> None:
@@ -223,6 +273,11 @@ def run_ours(args) -> None:
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
     }
+    try:
+        line["extra"] = {"mlp_train_step": _mlp_train_step_ms(world, dev, timed)}
+    except Exception as e:  # the headline line must not depend on the extra measurement
+        line["extra"] = {"mlp_train_step": {"error": repr(e)[:200]}}
+    _C.check_device_status()
     if rank == 0 and world == 1:
         val, cores, med = _cpu_sample(2048, 3)
         line["cpu_baseline"] = {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port",

@@ -1,0 +1,137 @@
+"""Column- and row-parallel TCFP-12 linear layers for 1/2/4/8 GPUs of one node.
+
+The reference has no distributed code; this follows the usual tensor-parallel
+split of a transformer block.  Column-parallel layers shard the output
+features (each rank quantizes and multiplies its own rows of W -- block scales
+are per (row, K block), so every quantized byte equals the unsharded layer's);
+row-parallel layers shard the input features on scale-block boundaries and sum
+their partial outputs with an all-reduce over NCCL (NVLink / NVSwitch).
+
+    y = RowParallel(act(ColumnParallel(x)))      # one all-reduce forward, one backward
+
+One process per GPU, ``torch.distributed`` for the plumbing.  The layer class
+is injectable so that the communication logic is testable on CPU with gloo.
+"""
+from __future__ import annotations
+
+from typing import Callable
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+
+def shard_bounds(size: int, world: int, rank: int, granule: int = 1) -> tuple[int, int]:
+    """[start, end) of ``rank``'s shard of ``size`` features, on multiples of
+    ``granule`` (the scale block), as even as the granules allow: 11008
+    features in blocks of 64 over 8 ranks gives four shards of 22 blocks and
+    four of 21."""
+    if size % granule != 0:
+        raise ValueError(f"size ({size}) must be divisible by the shard granule ({granule})")
+    units = size // granule
+    base, extra = divmod(units, world)
+    start = rank * base + min(rank, extra)
+    n = base + (1 if rank < extra else 0)
+    if n == 0:
+        raise ValueError(f"{size} features in granules of {granule} cannot be split over {world} ranks")
+    return start * granule, (start + n) * granule
+
+
+class _CopyToParallel(torch.autograd.Function):
+    """Identity forward; all-reduce of the gradient backward (input of a
+    column-parallel layer)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous()
+        if dist.is_initialized() and dist.get_world_size(ctx.group) > 1:
+            dist.all_reduce(g, op=dist.ReduceOp.SUM, group=ctx.group)
+        return g, None
+
+
+class _ReduceFromParallel(torch.autograd.Function):
+    """All-reduce forward (output of a row-parallel layer); identity backward."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        x = x.contiguous()
+        if dist.is_initialized() and dist.get_world_size(group) > 1:
+            dist.all_reduce(x, op=dist.ReduceOp.SUM, group=group)
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+def _default_factory(in_features: int, out_features: int, bias: bool, **kw) -> nn.Module:
+    from .nn import TCFPLinear
+
+    return TCFPLinear(in_features, out_features, bias=bias, use_tensor_cores=True, **kw)
+
+
+class ColumnParallelLinear(nn.Module):
+    """``y_local = x @ W[rows of this rank].T``; output stays sharded."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = True, *, group=None, granule: int = 16,
+                 layer_factory: Callable[..., nn.Module] = _default_factory, **layer_kw):
+        super().__init__()
+        self.group = group
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+        rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.out_start, self.out_end = shard_bounds(out_features, world, rank, granule)
+        self.in_features, self.out_features = in_features, out_features
+        self.inner = layer_factory(in_features, self.out_end - self.out_start, bias, **layer_kw)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.inner(_CopyToParallel.apply(x, self.group))
+
+
+class RowParallelLinear(nn.Module):
+    """``y = sum_ranks x[..., cols of this rank] @ W[:, cols].T`` (+ bias once)."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = True, *, group=None, granule: int = 16,
+                 layer_factory: Callable[..., nn.Module] = _default_factory, reduce_dtype: torch.dtype | None = None,
+                 **layer_kw):
+        super().__init__()
+        self.group = group
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+        rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.in_start, self.in_end = shard_bounds(in_features, world, rank, granule)
+        self.in_features, self.out_features = in_features, out_features
+        self.reduce_dtype = reduce_dtype
+        self.inner = layer_factory(self.in_end - self.in_start, out_features, False, **layer_kw)
+        # the bias is added after the reduction, once
+        self.bias = nn.Parameter(torch.zeros(out_features)) if bias else None
+
+    def forward(self, x_shard: torch.Tensor) -> torch.Tensor:
+        y = self.inner(x_shard)
+        if self.reduce_dtype is not None and y.dtype != self.reduce_dtype:
+            y = y.to(self.reduce_dtype)        # bf16 on the wire halves the NVLink bytes
+        y = _ReduceFromParallel.apply(y, self.group)
+        if self.bias is not None:
+            y = y + self.bias.to(y.dtype)
+        return y
+
+
+class ParallelMLP(nn.Module):
+    """``down(act(up(x)))`` with ``up`` column-parallel and ``down``
+    row-parallel: the hidden activation never leaves its rank."""
+
+    def __init__(self, d_model: int, d_hidden: int, *, group=None, granule: int = 16, bias: bool = True,
+                 activation: Callable[[torch.Tensor], torch.Tensor] = torch.nn.functional.gelu,
+                 layer_factory: Callable[..., nn.Module] = _default_factory, reduce_dtype=None, **layer_kw):
+        super().__init__()
+        self.up = ColumnParallelLinear(d_model, d_hidden, bias, group=group, granule=granule,
+                                       layer_factory=layer_factory, **layer_kw)
+        self.down = RowParallelLinear(d_hidden, d_model, bias, group=group, granule=granule,
+                                      layer_factory=layer_factory, reduce_dtype=reduce_dtype, **layer_kw)
+        self.activation = activation
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.down(self.activation(self.up(x)))

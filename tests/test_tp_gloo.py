@@ -1,0 +1,85 @@
+"""CPU, world size 2 over gloo: the tensor-parallel plumbing (shard bounds,
+gradient all-reduce of the column-parallel input, output all-reduce of the
+row-parallel layer) against an unsharded ``nn.Linear`` MLP.  The layer class is
+injected as plain ``nn.Linear`` so that no GPU is involved."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from tcfp_b200.tp import ParallelMLP, shard_bounds
+
+
+def test_shard_bounds_block_aligned_and_uneven():
+    spans = [shard_bounds(11008, 8, r, 64) for r in range(8)]
+    assert spans[0] == (0, 1408) and spans[-1][1] == 11008
+    assert [e - s for s, e in spans] == [1408] * 4 + [1344] * 4
+    assert all(s % 64 == 0 and e % 64 == 0 for s, e in spans)
+    assert all(spans[i][1] == spans[i + 1][0] for i in range(7))
+    assert shard_bounds(4096, 1, 0, 64) == (0, 4096)
+    with pytest.raises(ValueError):
+        shard_bounds(100, 2, 0, 64)
+    with pytest.raises(ValueError):
+        shard_bounds(64, 2, 1, 64)
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank: int, world: int, port: int, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.manual_seed(0)
+        d, h, granule = 32, 96, 16
+        ref_up = torch.nn.Linear(d, h)
+        ref_down = torch.nn.Linear(h, d)
+        x = torch.randn(8, d)
+        target = torch.randn(8, d)
+
+        factory = lambda i, o, b, **kw: torch.nn.Linear(i, o, bias=b)  # noqa: E731
+        mlp = ParallelMLP(d, h, granule=granule, layer_factory=factory)
+        s, e = mlp.up.out_start, mlp.up.out_end
+        assert (mlp.down.in_start, mlp.down.in_end) == (s, e)
+        with torch.no_grad():
+            mlp.up.inner.weight.copy_(ref_up.weight[s:e])
+            mlp.up.inner.bias.copy_(ref_up.bias[s:e])
+            mlp.down.inner.weight.copy_(ref_down.weight[:, s:e])
+            mlp.down.bias.copy_(ref_down.bias)
+
+        xr = x.clone().requires_grad_(True)
+        y_ref = ref_down(torch.nn.functional.gelu(ref_up(xr)))
+        ((y_ref - target) ** 2).mean().backward()
+
+        xp = x.clone().requires_grad_(True)
+        y = mlp(xp)
+        ((y - target) ** 2).mean().backward()
+
+        ok = torch.allclose(y, y_ref, atol=1e-5)
+        ok &= torch.allclose(xp.grad, xr.grad, atol=1e-5)                       # all-reduced dX
+        ok &= torch.allclose(mlp.up.inner.weight.grad, ref_up.weight.grad[s:e], atol=1e-5)
+        ok &= torch.allclose(mlp.down.inner.weight.grad, ref_down.weight.grad[:, s:e], atol=1e-5)
+        ok &= torch.allclose(mlp.down.bias.grad, ref_down.bias.grad, atol=1e-5)
+        ret[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_parallel_mlp_matches_unsharded_world2():
+    world = 2
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, ret)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert all(ret.get(r) for r in range(world)), dict(ret)
