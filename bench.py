@@ -263,10 +263,11 @@ def run_ours(args) -> None:
                    "parallelism": f"column-parallel shards x{world}, no collective" if world > 1 else "single GPU"},
         "pct_of_nominal_fp8_peak": per_gpu / 4500.0,
         "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": fp8_peak, "unit": "TFLOP/s",
-                     "frac": per_gpu / fp8_peak, "traffic": None,
+                     "frac": per_gpu / fp8_peak, "traffic": 880.0e6,
+                     "traffic_note": "dram__bytes_read+write per launch from ncu on this workload (profiles/dual_gemm_pair_mxf8_8192_bench.md); algorithmic 448 MB",
                      "peak_source": f"2 x {peaks['src']} cuBLAS bf16 burst ({peaks['bf16']} TFLOP/s): no FP8 peak was measured; "
                                     "FP8 tensor rate is twice the bf16 rate",
-                     "kernel": "dual_gemm_kernel<KIND_MXF8>", "flop_per_launch": FLOP_PER_STEP},
+                     "kernel": "dual_gemm_pair_kernel<KIND_MXF8>", "flop_per_launch": FLOP_PER_STEP},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 4,
                 "ms_per_step": e2e_ms / e2e_steps,
                 "path": "pinned host X -> H2D -> fused_dual_quantize_fp8(W, EF) -> block_quantize_fp8(X) -> dual GEMM -> D2H out"},
