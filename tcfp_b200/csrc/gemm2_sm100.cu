@@ -149,7 +149,7 @@ __device__ __forceinline__ void tile_coords2(int tile, int tiles_m, int tiles_n,
   nb = in_group / gm;
 }
 
-template <int KIND, bool B_MN, bool OUT_BF16>
+template <int KIND, bool B_MN, bool OUT_BF16, bool A_MN = false>
 __global__ void __launch_bounds__(kThreads, 1)
 dual_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_bhi,
                       const __grid_constant__ CUtensorMap tm_blo, const __grid_constant__ CUtensorMap tm_out,
@@ -236,7 +236,15 @@ dual_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
           const uint32_t sa = smem_u32(stage_base + stage * kStageBytes);
           const uint32_t sb = sa + kATile;
           const int k0 = ks * T::kStageK;
-          tma_load_2d_pair(sa, &tm_a, k0, row0, full_leader);
+          if constexpr (!A_MN) {
+            tma_load_2d_pair(sa, &tm_a, k0, row0, full_leader);
+          } else {
+            // A stored transposed, (K, M) row-major: one box per 128-byte-wide group of its M columns
+            constexpr int kABoxes = T::kElemBytes;
+#pragma unroll
+            for (int b = 0; b < kABoxes; ++b)
+              tma_load_2d_pair(sa + b * (kATile / kABoxes), &tm_a, row0 + b * (128 / T::kElemBytes), k0, full_leader);
+          }
           if constexpr (!kSum) {
             // this CTA's half of the 256 MMA columns
             const CUtensorMap* map = (p.has_lo && rank == 1) ? &tm_blo : &tm_bhi;
@@ -278,9 +286,12 @@ dual_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
       } else {
         const uint32_t fa = (KIND == KIND_BF16) ? 1u : (uint32_t)p.a_fmt;
         const uint32_t fb = (KIND == KIND_BF16) ? 1u : 0u;
-        idesc = (1u << 4) | (fa << 7) | (fb << 10) | ((B_MN ? 1u : 0u) << 16) | ((n_mma >> 3) << 17) |
-                ((uint32_t)((2 * BM) >> 4) << 24);
+        idesc = (1u << 4) | (fa << 7) | (fb << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
+                ((n_mma >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
       }
+      static_assert(!(A_MN && KIND == KIND_MXF8), "block-scaled kind takes A K-major");
+      constexpr uint32_t kALbo = A_MN ? (uint32_t)(kATile / T::kElemBytes) : 16u;
+      constexpr uint32_t kAKStep = A_MN ? (uint32_t)(T::kMmaK * 128) : 32u;
       // B: every CTA holds (n_mma / 2) columns of each MMA's B operand.
       //   K-major : rows of 128 B, 8-row groups 1024 B apart.
       //   MN-major: one 128-byte-wide column group (CONCAT fp8: 128 cols; SUM bf16: 64 cols); LBO unused.
@@ -316,7 +327,7 @@ dual_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
           }
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const uint64_t adesc = make_desc(sa + j * 32, 16, 1024, 2);
+            const uint64_t adesc = make_desc(sa + j * kAKStep, kALbo, 1024, 2);
             uint32_t id = idesc;
             if constexpr (KIND == KIND_MXF8) {
               const uint32_t sfid = (uint32_t)(sf_first + (j >> sf_shift));
@@ -489,7 +500,7 @@ int make_map2(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const vo
   return TCFP_OK;
 }
 
-template <int KIND, bool B_MN, bool OUT_BF16>
+template <int KIND, bool B_MN, bool OUT_BF16, bool A_MN = false>
 int launch2(const void* a, const void* b_hi, const void* b_lo, const void* sf_a, const void* sf_hi, const void* sf_lo,
             void* out, Gemm2Params p, cudaStream_t stream) {
   using T = Traits2<KIND>;
@@ -498,7 +509,9 @@ int launch2(const void* a, const void* b_hi, const void* b_lo, const void* sf_a,
   const CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_128B;
   CUtensorMap tm_a, tm_bhi, tm_blo, tm_out, tm_sfa, tm_sfhi, tm_sflo;
   int rc;
-  if ((rc = make_map2(&tm_a, dt, eb, a, p.M, p.K, T::kStageK, BM, sw)) != TCFP_OK) return rc;
+  if (!A_MN) rc = make_map2(&tm_a, dt, eb, a, p.M, p.K, T::kStageK, BM, sw);
+  else rc = make_map2(&tm_a, dt, eb, a, p.K, p.M, 128 / eb, T::kStageK, sw);
+  if (rc != TCFP_OK) return rc;
   const int b_rows = T::kSum ? BN / 2 : BN;    // B rows (columns of the output) one CTA stages per operand
   if (!B_MN) {
     if ((rc = make_map2(&tm_bhi, dt, eb, b_hi, p.N, p.K, T::kStageK, b_rows, sw)) != TCFP_OK) return rc;
@@ -526,7 +539,7 @@ int launch2(const void* a, const void* b_hi, const void* b_lo, const void* sf_a,
   p.k_stages = (p.K + T::kStageK - 1) / T::kStageK;
   p.has_lo = b_lo != nullptr;
   constexpr int smem = smem_bytes2<KIND>();
-  auto kern = dual_gemm_pair_kernel<KIND, B_MN, OUT_BF16>;
+  auto kern = dual_gemm_pair_kernel<KIND, B_MN, OUT_BF16, A_MN>;
   static bool configured = false;
   if (!configured) {
     CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -555,7 +568,7 @@ int launch2(const void* a, const void* b_hi, const void* b_lo, const void* sf_a,
 }  // namespace
 
 // Entry points used by the C ABI functions in gemm_sm100.cu.  kind: KIND_*.
-int pair_gemm_dispatch(int kind, bool b_mn, bool out_bf16, const void* a, const void* b_hi, const void* b_lo,
+int pair_gemm_dispatch(int kind, bool a_mn, bool b_mn, bool out_bf16, const void* a, const void* b_hi, const void* b_lo,
                        const void* sf_a, const void* sf_hi, const void* sf_lo, void* out, int M, int N, int K, int a_fmt,
                        int block_size, const float* s_a, const float* s_hi, const float* s_lo, const float* bias,
                        cudaStream_t stream) {
@@ -567,6 +580,11 @@ int pair_gemm_dispatch(int kind, bool b_mn, bool out_bf16, const void* a, const 
 #define TCFP_PAIR(KIND, BMN)                                                                              \
   return out_bf16 ? launch2<KIND, BMN, true>(a, b_hi, b_lo, sf_a, sf_hi, sf_lo, out, p, stream)           \
                   : launch2<KIND, BMN, false>(a, b_hi, b_lo, sf_a, sf_hi, sf_lo, out, p, stream)
+  if (a_mn) {
+    if (kind != KIND_F8 || !b_mn) return fail(TCFP_ERR_UNSUPPORTED, "pair kernel: transposed A is built for the FP8 weight gradient only");
+    return out_bf16 ? launch2<KIND_F8, true, true, true>(a, b_hi, b_lo, sf_a, sf_hi, sf_lo, out, p, stream)
+                    : launch2<KIND_F8, true, false, true>(a, b_hi, b_lo, sf_a, sf_hi, sf_lo, out, p, stream);
+  }
   if (kind == KIND_F8) { if (b_mn) { TCFP_PAIR(KIND_F8, true); } else { TCFP_PAIR(KIND_F8, false); } }
   if (kind == KIND_MXF8) { TCFP_PAIR(KIND_MXF8, false); }
   if (kind == KIND_BF16) { if (b_mn) { TCFP_PAIR(KIND_BF16, true); } else { TCFP_PAIR(KIND_BF16, false); } }

@@ -522,7 +522,7 @@ extern "C" int32_t tcfp_dual_gemm(const uint8_t* a, int32_t a_fmt, const uint8_t
   p.s_a = s_a; p.s_hi = s_hi; p.s_lo = s_lo; p.bias = bias;
   const bool obf = out_dtype == TCFP_BF16;
   if (use_pair_kernel(M))
-    return pair_gemm_dispatch(KIND_F8, trans_b != 0, obf, a, w_hi, w_lo, nullptr, nullptr, nullptr, out, (int)M, (int)N,
+    return pair_gemm_dispatch(KIND_F8, false, trans_b != 0, obf, a, w_hi, w_lo, nullptr, nullptr, nullptr, out, (int)M, (int)N,
                               (int)K, a_fmt, 0, s_a, s_hi, s_lo, bias, stream);
   if (!trans_b) return obf ? launch<KIND_F8, false, true>(a, w_hi, w_lo, out, p, stream)
                            : launch<KIND_F8, false, false>(a, w_hi, w_lo, out, p, stream);
@@ -543,6 +543,9 @@ extern "C" int32_t tcfp_dw_gemm(const uint8_t* g, int32_t g_fmt, const uint8_t* 
   p.M = (int)n_out; p.N = (int)k_in; p.K = (int)tokens;
   p.a_fmt = g_fmt;
   p.s_a = s_g; p.s_hi = s_x;
+  if (use_pair_kernel(n_out))
+    return pair_gemm_dispatch(KIND_F8, true, true, out_dtype == TCFP_BF16, g, x, nullptr, nullptr, nullptr, nullptr, out,
+                              (int)n_out, (int)k_in, (int)tokens, g_fmt, 0, s_g, s_x, nullptr, nullptr, stream);
   return out_dtype == TCFP_BF16 ? launch<KIND_F8, true, true, true>(g, x, nullptr, out, p, stream)
                                 : launch<KIND_F8, true, false, true>(g, x, nullptr, out, p, stream);
 }
@@ -569,7 +572,7 @@ extern "C" int32_t tcfp_block_dual_gemm(const uint8_t* a, const uint8_t* sf_a, c
   p.bias = bias;
   p.sf_a = sf_a; p.sf_hi = sf_hi; p.sf_lo = sf_lo;
   if (use_pair_kernel(M))
-    return pair_gemm_dispatch(KIND_MXF8, false, out_dtype == TCFP_BF16, a, w_hi, w_lo, sf_a, sf_hi, sf_lo, out, (int)M,
+    return pair_gemm_dispatch(KIND_MXF8, false, false, out_dtype == TCFP_BF16, a, w_hi, w_lo, sf_a, sf_hi, sf_lo, out, (int)M,
                               (int)N, (int)K, TCFP_E4M3, block_size, nullptr, nullptr, nullptr, bias, stream);
   return out_dtype == TCFP_BF16 ? launch<KIND_MXF8, false, true>(a, w_hi, w_lo, out, p, stream)
                                 : launch<KIND_MXF8, false, false>(a, w_hi, w_lo, out, p, stream);
@@ -588,7 +591,7 @@ extern "C" int32_t tcfp_bf16_dual_gemm(const void* a, const void* b_hi, const vo
   p.bias = bias;
   const bool obf = out_dtype == TCFP_BF16;
   if (use_pair_kernel(M))
-    return pair_gemm_dispatch(KIND_BF16, trans_b != 0, obf, a, b_hi, b_lo, nullptr, nullptr, nullptr, out, (int)M, (int)N,
+    return pair_gemm_dispatch(KIND_BF16, false, trans_b != 0, obf, a, b_hi, b_lo, nullptr, nullptr, nullptr, out, (int)M, (int)N,
                               (int)K, 0, 0, nullptr, nullptr, nullptr, bias, stream);
   if (!trans_b) return obf ? launch<KIND_BF16, false, true>(a, b_hi, b_lo, out, p, stream)
                            : launch<KIND_BF16, false, false>(a, b_hi, b_lo, out, p, stream);

@@ -177,7 +177,7 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes
 
 
 // Two-SM (CTA pair) form of the dual GEMM, defined in gemm2_sm100.cu.
-int pair_gemm_dispatch(int kind, bool b_mn, bool out_bf16, const void* a, const void* b_hi, const void* b_lo,
+int pair_gemm_dispatch(int kind, bool a_mn, bool b_mn, bool out_bf16, const void* a, const void* b_hi, const void* b_lo,
                        const void* sf_a, const void* sf_hi, const void* sf_lo, void* out, int M, int N, int K, int a_fmt,
                        int block_size, const float* s_a, const float* s_hi, const float* s_lo, const float* bias,
                        cudaStream_t stream);

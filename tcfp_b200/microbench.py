@@ -1,0 +1,118 @@
+"""Kernel micro-benchmarks (CUDA events, inputs larger than L2 at the default
+sizes).  Used to time single kernels and as the target of ncu captures:
+
+    python -m tcfp_b200.microbench gemm   [N]   # per-tensor dual / single GEMM, N^3
+    python -m tcfp_b200.microbench block  [N]   # block-scaled dual GEMM fwd + dX, N^3, block 32/64/128
+    python -m tcfp_b200.microbench quant  [N]   # block and per-tensor quantizers on N x N
+    python -m tcfp_b200.microbench lib    [N]   # library comparators: torch._scaled_mm, bf16 matmul
+"""
+from __future__ import annotations
+
+import sys
+
+import torch
+
+DEV = "cuda"
+
+
+def timeit(fn, iters=20, warmup=3) -> float:
+    for _ in range(warmup):
+        fn()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def _fp8(n, m, dtype=torch.float8_e4m3fn):
+    return torch.randn(n, m, device=DEV).to(dtype)
+
+
+def gemm(n: int) -> None:
+    from .kernels import fp8_weight_grad, fused_dual_gemm_backward_dx, fused_dual_gemm_forward
+
+    a, hi, lo = _fp8(n, n), _fp8(n, n), _fp8(n, n)
+    g = _fp8(n, n, torch.float8_e5m2)
+    s = torch.ones(1, device=DEV)
+    ms = timeit(lambda: fused_dual_gemm_forward(a, hi, lo, s, s, s))
+    print(f"dual GEMM fwd  {n}^3: {ms:.3f} ms  {4 * n**3 / ms / 1e9:.0f} TFLOP/s (both products)")
+    ms = timeit(lambda: fused_dual_gemm_backward_dx(g, hi, lo, s, s, s))
+    print(f"dual GEMM dX   {n}^3: {ms:.3f} ms  {4 * n**3 / ms / 1e9:.0f} TFLOP/s (both products)")
+    ms = timeit(lambda: fused_dual_gemm_forward(a, hi, None, s, s, None))
+    print(f"single GEMM    {n}^3: {ms:.3f} ms  {2 * n**3 / ms / 1e9:.0f} TFLOP/s")
+    ms = timeit(lambda: fp8_weight_grad(g, a, s, s))
+    print(f"dW GEMM (g^T x) {n}^3: {ms:.3f} ms  {2 * n**3 / ms / 1e9:.0f} TFLOP/s")
+
+
+def block(n: int) -> None:
+    from .kernels import (block_quantize_fp8, fused_block_scaled_backward_dx, fused_block_scaled_dual_gemm_forward,
+                          fused_dual_quantize_fp8)
+
+    x = torch.randn(n, n, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(n, n, device=DEV) * 0.02
+    gy = torch.randn(n, n, device=DEV)
+    for bs in (32, 64, 128):
+        hi, lo, sh, sl = fused_dual_quantize_fp8(w, bs)
+        a, sa = block_quantize_fp8(x, bs)
+        ms = timeit(lambda: fused_block_scaled_dual_gemm_forward(a, hi, lo, sa, sh, sl, bs))
+        print(f"block-{bs} dual GEMM fwd {n}^3: {ms:.3f} ms  {4 * n**3 / ms / 1e9:.0f} TFLOP/s (both products)")
+        gq, sg, gb = block_quantize_fp8(gy, bs, torch.float8_e5m2, want_bf16=True)
+        ms = timeit(lambda: fused_block_scaled_backward_dx(gq, hi, lo, sg, sh, sl, bs, grad_bf16=gb))
+        print(f"block-{bs} dX (dequant + bf16 GEMM) {n}^3: {ms:.3f} ms  {4 * n**3 / ms / 1e9:.0f} TFLOP/s (both products)")
+
+
+def quant(n: int) -> None:
+    from .core import dual_quantize_per_tensor, to_fp8_e4m3, to_fp8_e5m2
+    from .kernels import block_quantize_fp8, fused_dual_quantize_fp8
+
+    w = torch.randn(n, n, device=DEV) * 0.02
+    err = torch.zeros(n, n, device=DEV)
+    x = torch.randn(n, n, device=DEV, dtype=torch.bfloat16)
+    gy = torch.randn(n, n, device=DEV)
+    e = n * n
+
+    def report(name, ms, bytes_per_elem):
+        print(f"{name:<46s} {ms * 1e3:8.1f} us  {bytes_per_elem * e / ms / 1e6:7.0f} GB/s ({bytes_per_elem} B/elem algorithmic)")
+
+    for bs in (32, 64, 128):
+        report(f"dual_quantize block-{bs} EF", timeit(lambda: fused_dual_quantize_fp8(w, bs, err)), 14)
+    report("dual_quantize block-64 no EF", timeit(lambda: fused_dual_quantize_fp8(w, 64, None)), 6)
+    report("dual_quantize block-64 SRR", timeit(lambda: fused_dual_quantize_fp8(w, 64, None, True, seed=1)), 6)
+    report("block_quantize bf16 -> E4M3 block-64", timeit(lambda: block_quantize_fp8(x, 64)), 3)
+    report("block_quantize f32 -> E5M2 (+bf16 copy) block-64",
+           timeit(lambda: block_quantize_fp8(gy, 64, torch.float8_e5m2, want_bf16=True)), 7)
+    report("dual_quantize per-tensor EF (3 passes)", timeit(lambda: dual_quantize_per_tensor(w, err)), 14)
+    a_hi = torch.tensor(0.1, device=DEV)
+    a_lo = torch.tensor(0.0125, device=DEV)
+    report("dual_quantize per-tensor EF, amax given (1 pass)",
+           timeit(lambda: dual_quantize_per_tensor(w, err, amax_hi=a_hi, amax_lo=a_lo)), 14)
+    report("dual_quantize per-tensor SRR", timeit(lambda: dual_quantize_per_tensor(w, None, srr=True)), 6)
+    report("to_fp8_e4m3 bf16 (2 passes)", timeit(lambda: to_fp8_e4m3(x)), 3)
+    report("to_fp8_e5m2 f32 (2 passes)", timeit(lambda: to_fp8_e5m2(gy)), 5)
+
+
+def lib(n: int) -> None:
+    a, hi, lo = _fp8(n, n), _fp8(n, n), _fp8(n, n)
+    s = torch.ones(1, device=DEV)
+    mm = lambda w, dt: torch._scaled_mm(a, w.t(), scale_a=s, scale_b=s, out_dtype=dt)  # noqa: E731
+    ms = timeit(lambda: mm(hi, torch.float32))
+    print(f"torch._scaled_mm fp8->f32  {n}^3: {ms:.3f} ms  {2 * n**3 / ms / 1e9:.0f} TFLOP/s")
+    ms = timeit(lambda: mm(hi, torch.bfloat16))
+    print(f"torch._scaled_mm fp8->bf16 {n}^3: {ms:.3f} ms  {2 * n**3 / ms / 1e9:.0f} TFLOP/s")
+    ms = timeit(lambda: mm(hi, torch.float32) + mm(lo, torch.float32))
+    print(f"2 x _scaled_mm + add (the reference's fallback, tcfp/nn/__init__.py:405-421) {n}^3: {ms:.3f} ms  "
+          f"{4 * n**3 / ms / 1e9:.0f} TFLOP/s (both products)")
+    x = torch.randn(n, n, device=DEV, dtype=torch.bfloat16)
+    y = torch.randn(n, n, device=DEV, dtype=torch.bfloat16)
+    ms = timeit(lambda: x @ y)
+    print(f"bf16 matmul {n}^3: {ms:.3f} ms  {2 * n**3 / ms / 1e9:.0f} TFLOP/s")
+
+
+if __name__ == "__main__":
+    what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
+    size = int(sys.argv[2]) if len(sys.argv) > 2 else 8192
+    {"gemm": gemm, "block": block, "quant": quant, "lib": lib}[what](size)
