@@ -70,11 +70,11 @@ __device__ __forceinline__ float amax4(const f4& x) {
 
 // Writes the staged exponents of one tile: planes (K/bs, rows) and, when
 // requested, the packed E8M0 chunks.
-template <int BS>
+template <int BS, int TILE_COLS = kTileCols>
 __device__ __forceinline__ void flush_tile_scales(const int8_t (*s_exp)[kTileRows], int8_t* plane,
                                                   uint8_t* sf, int64_t rows, int64_t K, int64_t row0,
                                                   int64_t col0) {
-  constexpr int kBlocksPerTile = kTileCols / BS;
+  constexpr int kBlocksPerTile = TILE_COLS / BS;
   const int64_t num_kb = K / BS;
   const int64_t kb0 = col0 / BS;
   const int r = threadIdx.x & 31;
@@ -103,7 +103,7 @@ __device__ __forceinline__ void flush_tile_scales(const int8_t (*s_exp)[kTileRow
 // K1a: block-scaled dual quantizer
 // ---------------------------------------------------------------------------
 template <int BS, bool W_BF16, int MODE>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 4)
 dual_quantize_block_kernel(const void* __restrict__ w, float* err, uint8_t* __restrict__ w_hi,
                            uint8_t* __restrict__ w_lo, int8_t* __restrict__ exp_hi,
                            int8_t* __restrict__ exp_lo, uint8_t* __restrict__ sf_hi,
@@ -207,63 +207,88 @@ dual_quantize_block_kernel(const void* __restrict__ w, float* err, uint8_t* __re
 
 // ---------------------------------------------------------------------------
 // K2: block-scaled single quantizer (activations E4M3, gradients E5M2)
+// One 128-bit load per lane: 4 float32 or 8 bfloat16 values, so a tile is 512
+// or 1024 columns wide and a scale block is a group of BS/4 or BS/8 lanes.
 // ---------------------------------------------------------------------------
 template <int BS, bool X_BF16, bool E5M2>
 __global__ void __launch_bounds__(kThreads)
 quantize_block_kernel(const void* __restrict__ x, uint8_t* __restrict__ out, int8_t* __restrict__ exps,
                       uint8_t* __restrict__ sf, __nv_bfloat16* __restrict__ deq, int64_t R, int64_t C) {
-  constexpr int GROUP = BS / 4;
-  constexpr int kBlocksPerTile = kTileCols / BS;
+  constexpr int VEC = X_BF16 ? 8 : 4;
+  constexpr int GROUP = BS / VEC;
+  constexpr int SEG = 32 * VEC;             // columns one warp covers per load
+  constexpr int TILE_COLS = 4 * SEG;
+  constexpr int kBlocksPerTile = TILE_COLS / BS;
   __shared__ int8_t s_e[kBlocksPerTile][kTileRows];
 
-  const int64_t tiles_c = (C + kTileCols - 1) / kTileCols;
+  const int64_t tiles_c = (C + TILE_COLS - 1) / TILE_COLS;
   const int64_t row0 = (int64_t)(blockIdx.x / tiles_c) * kTileRows;
-  const int64_t col0 = (int64_t)(blockIdx.x % tiles_c) * kTileCols;
+  const int64_t col0 = (int64_t)(blockIdx.x % tiles_c) * TILE_COLS;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
 #pragma unroll 1
   for (int rr = 0; rr < 4; ++rr) {
     const int r_local = warp * 4 + rr;
     const int64_t row = row0 + r_local;
-    f4 xv[4];
+    float xv[4][VEC];
     bool ok[4];
 #pragma unroll
     for (int s = 0; s < 4; ++s) {
-      const int64_t col = col0 + s * 128 + lane * 4;
+      const int64_t col = col0 + s * SEG + lane * VEC;
       ok[s] = (row < R) && (col < C);
       if (ok[s]) {
-        xv[s] = load4<X_BF16>(x, (size_t)row * C + col);
+        if constexpr (X_BF16) {
+          uint4 raw = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(x) + (size_t)row * C + col));
+          const uint32_t wds[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            xv[s][2 * i] = __uint_as_float(wds[i] << 16);
+            xv[s][2 * i + 1] = __uint_as_float(wds[i] & 0xFFFF0000u);
+          }
+        } else {
+          float4 raw = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + (size_t)row * C + col));
+          xv[s][0] = raw.x; xv[s][1] = raw.y; xv[s][2] = raw.z; xv[s][3] = raw.w;
+        }
       } else {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) xv[s].v[i] = 0.f;
+        for (int i = 0; i < VEC; ++i) xv[s][i] = 0.f;
       }
     }
 #pragma unroll
     for (int s = 0; s < 4; ++s) {
-      const int64_t col = col0 + s * 128 + lane * 4;
-      const int e = block_exponent_fast<E5M2>(group_max<GROUP>(amax4(xv[s])));
+      const int64_t col = col0 + s * SEG + lane * VEC;
+      float am = 0.f;
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) am = fmaxf(am, fabsf(xv[s][i]));
+      const int e = block_exponent_fast<E5M2>(group_max<GROUP>(am));
       const float fwd = exp2_int(-e), inv = exp2_int(e);
-      const uint32_t pc = encode_fp8x2<E5M2>(__fmul_rn(xv[s].v[0], fwd), __fmul_rn(xv[s].v[1], fwd)) |
-                          (encode_fp8x2<E5M2>(__fmul_rn(xv[s].v[2], fwd), __fmul_rn(xv[s].v[3], fwd)) << 16);
+      uint32_t pc[VEC / 4];
+#pragma unroll
+      for (int h = 0; h < VEC / 4; ++h)
+        pc[h] = encode_fp8x2<E5M2>(__fmul_rn(xv[s][4 * h], fwd), __fmul_rn(xv[s][4 * h + 1], fwd)) |
+                (encode_fp8x2<E5M2>(__fmul_rn(xv[s][4 * h + 2], fwd), __fmul_rn(xv[s][4 * h + 3], fwd)) << 16);
       if (ok[s]) {
         const size_t idx = (size_t)row * C + col;
-        *reinterpret_cast<uint32_t*>(out + idx) = pc;
+        if constexpr (VEC == 8) *reinterpret_cast<uint2*>(out + idx) = make_uint2(pc[0], pc[1]);
+        else *reinterpret_cast<uint32_t*>(out + idx) = pc[0];
         if (deq != nullptr) {
-          __nv_bfloat162 p0 = __floats2bfloat162_rn(__fmul_rn(decode_fp8_fast<E5M2>(pc), inv),
-                                                   __fmul_rn(decode_fp8_fast<E5M2>(pc >> 8), inv));
-          __nv_bfloat162 p1 = __floats2bfloat162_rn(__fmul_rn(decode_fp8_fast<E5M2>(pc >> 16), inv),
-                                                   __fmul_rn(decode_fp8_fast<E5M2>(pc >> 24), inv));
-          uint2 pk;
-          pk.x = *reinterpret_cast<uint32_t*>(&p0);
-          pk.y = *reinterpret_cast<uint32_t*>(&p1);
-          *reinterpret_cast<uint2*>(deq + idx) = pk;
+          uint32_t dq[VEC / 2];
+#pragma unroll
+          for (int i = 0; i < VEC / 2; ++i) {
+            const uint32_t word = pc[i / 2] >> (16 * (i & 1));
+            __nv_bfloat162 pr = __floats2bfloat162_rn(__fmul_rn(decode_fp8_fast<E5M2>(word), inv),
+                                                     __fmul_rn(decode_fp8_fast<E5M2>(word >> 8), inv));
+            dq[i] = *reinterpret_cast<uint32_t*>(&pr);
+          }
+          if constexpr (VEC == 8) *reinterpret_cast<uint4*>(deq + idx) = make_uint4(dq[0], dq[1], dq[2], dq[3]);
+          else *reinterpret_cast<uint2*>(deq + idx) = make_uint2(dq[0], dq[1]);
         }
       }
-      if ((lane % GROUP) == 0) s_e[(s * 128 + lane * 4) / BS][r_local] = (int8_t)e;
+      if ((lane % GROUP) == 0) s_e[(s * SEG + lane * VEC) / BS][r_local] = (int8_t)e;
     }
   }
   __syncthreads();
-  flush_tile_scales<BS>(s_e, exps, sf, R, C, row0, col0);
+  flush_tile_scales<BS, TILE_COLS>(s_e, exps, sf, R, C, row0, col0);
 }
 
 // exponent plane -> packed chunks, one thread per (row, k_group)
@@ -689,6 +714,8 @@ extern "C" int32_t tcfp_quantize(const void* x, int32_t x_dtype, uint8_t* out, v
   const bool bf16 = (x_dtype == TCFP_BF16), e5m2 = (fmt == TCFP_E5M2);
   if (C % 4 != 0 || ((uintptr_t)x & (bf16 ? 7 : 15)) || ((uintptr_t)out & 3))
     return fail(TCFP_ERR_INVALID, "quantize: tensors must be contiguous, aligned, C %% 4 == 0");
+  if (block_size != 0 && bf16 && (((uintptr_t)x & 15) || ((uintptr_t)out & 7) || ((uintptr_t)deq_bf16_out & 15)))
+    return fail(TCFP_ERR_INVALID, "quantize: bfloat16 block quantization needs 16-byte aligned tensors");
   if (stochastic && (block_size != 0 || e5m2))
     return fail(TCFP_ERR_UNSUPPORTED, "quantize: stochastic rounding is per-tensor E4M3 only");
   if (block_size != 0) {
@@ -698,7 +725,8 @@ extern "C" int32_t tcfp_quantize(const void* x, int32_t x_dtype, uint8_t* out, v
       return fail(TCFP_ERR_INVALID, "K (%lld) must be divisible by block_size (%d)", (long long)C, block_size);
     if (sf_out && ((C / block_size) % 4 != 0))
       CUDA_TRY(cudaMemsetAsync(sf_out, 127, tcfp_sf_packed_bytes(R, C, block_size), stream));
-    const int64_t tiles = ((R + kTileRows - 1) / kTileRows) * ((C + kTileCols - 1) / kTileCols);
+    const int64_t tile_cols = bf16 ? 2 * kTileCols : kTileCols;
+    const int64_t tiles = ((R + kTileRows - 1) / kTileRows) * ((C + tile_cols - 1) / tile_cols);
     if (tiles > 0x7FFFFFFF) return fail(TCFP_ERR_UNSUPPORTED, "quantize: tensor too large");
     DISPATCH_BS(block_size, DISPATCH_BOOL(bf16, X_BF16, DISPATCH_BOOL(e5m2, E5M2,
       quantize_block_kernel<BS, X_BF16, E5M2><<<(unsigned)tiles, kThreads, 0, stream>>>(

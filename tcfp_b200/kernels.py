@@ -234,7 +234,7 @@ def fused_dual_quantize_fp8(weight, block_size=128, error_buf=None, stochastic_l
 
 def fused_block_scaled_dual_gemm_forward(act_fp8, w_hi_fp8, w_lo_fp8, act_scales, w_hi_scales, w_lo_scales,
                                          block_size, sparse_threshold=0.0, persistent=True, launch_mult=1, *,
-                                         bias=None, out_dtype=torch.float32):
+                                         bias=None, out_dtype=torch.float32, out=None):
     """Block-scaled 2-GEMM forward (tcfp/kernels.py:1939-2028).  The tuning
     arguments of the reference are accepted and ignored: the kernel is always
     persistent with one CTA per SM."""
@@ -247,7 +247,10 @@ def fused_block_scaled_dual_gemm_forward(act_fp8, w_hi_fp8, w_lo_fp8, act_scales
     sf_a = pack_block_scales(act_scales, block_size)
     sf_hi = pack_block_scales(w_hi_scales, block_size)
     sf_lo = pack_block_scales(w_lo_scales, block_size) if w_lo_fp8 is not None else None
-    out = torch.empty((M, N), device=act_fp8.device, dtype=out_dtype)
+    if out is None:
+        out = torch.empty((M, N), device=act_fp8.device, dtype=out_dtype)
+    else:
+        assert out.shape == (M, N) and out.dtype == out_dtype and out.is_contiguous(), "bad out buffer"
     _C.check(_C.load().tcfp_block_dual_gemm(
         _C.ptr(act_fp8), _C.ptr(sf_a), _C.ptr(w_hi_fp8), _C.ptr(sf_hi), _C.ptr(w_lo_fp8), _C.ptr(sf_lo),
         _C.ptr(bias), _C.ptr(out), _out_code(out_dtype), M, N, K, block_size, _C.stream()))

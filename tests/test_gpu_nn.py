@@ -183,3 +183,25 @@ def test_fp8_weight_grad_kernel():
         ref = (gq.float().t() @ xq.float()) * (ig * ix)
         out = fp8_weight_grad(gq.to(DEV), xq.to(DEV), ig.to(DEV), ix.to(DEV))
         assert out.shape == (N, K) and rel_fro(out, ref) <= 1e-3
+
+
+def test_host_streamed_linear_matches_unchunked():
+    from tcfp_b200.host_pipeline import HostStreamedLinear
+    from tcfp_b200.kernels import block_quantize_fp8, fused_block_scaled_dual_gemm_forward, fused_dual_quantize_fp8
+
+    M, K, N, bs = 1000, 512, 384, 64
+    w = weights(950, N, K, outliers=True).to(DEV)
+    x_host = acts(951, M, K, torch.bfloat16).pin_memory()
+    out_host = torch.empty(M, N, dtype=torch.float32).pin_memory()
+    lin = HostStreamedLinear(w, bs, chunks=3)
+    for step in range(2):       # second call exercises buffer reuse and a non-zero error buffer
+        err = lin.err.clone()
+        lin.forward_from_host(x_host, out_host)
+        torch.cuda.synchronize()
+        hi, lo, sh, sl = fused_dual_quantize_fp8(w, bs, err)
+        a, sa = block_quantize_fp8(x_host.to(DEV), bs)
+        want = fused_block_scaled_dual_gemm_forward(a, hi, lo, sa, sh, sl, bs)
+        # chunks shorter than 256 rows run on the one-SM kernel, which sums hi and lo in the epilogue
+        # instead of in the accumulator: same products, different FP32 summation order
+        assert rel_fro(out_host, want) <= 1e-5
+        assert torch.equal(lin.err, err)
