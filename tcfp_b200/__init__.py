@@ -11,6 +11,8 @@ from .core import (  # noqa: F401
     absmax,
     dual_quantize_per_tensor,
     ensure_column_major,
+    fp8_matmul,
+    fp8_matmul_nn,
     to_fp8_e4m3,
     to_fp8_e4m3_sr,
     to_fp8_e5m2,

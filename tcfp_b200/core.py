@@ -130,6 +130,26 @@ def ensure_column_major(t: torch.Tensor) -> torch.Tensor:
     return t.t().contiguous().t()
 
 
+def fp8_matmul(a_fp8: torch.Tensor, b_fp8: torch.Tensor, scale_a: torch.Tensor, scale_b: torch.Tensor,
+               out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """``(a * scale_a) @ (b * scale_b)`` for ``a (M,K)``, ``b (K,N)`` FP8 with
+    scalar inverse scales (tcfp/core.py:519-553) -- the single-operand form of
+    the dual GEMM, reading ``b`` in place."""
+    from .kernels import fused_dual_gemm_backward_dx
+
+    return fused_dual_gemm_backward_dx(a_fp8.contiguous(), b_fp8.contiguous(), None, scale_a.reshape(1),
+                                       scale_b.reshape(1), None, out_dtype=out_dtype)
+
+
+def fp8_matmul_nn(a_fp8: torch.Tensor, b_fp8_t: torch.Tensor, scale_a: torch.Tensor, scale_b: torch.Tensor,
+                  out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """Same with ``b`` given transposed, ``(N, K)`` (tcfp/core.py:556-578)."""
+    from .kernels import fused_dual_gemm_forward
+
+    return fused_dual_gemm_forward(a_fp8.contiguous(), b_fp8_t.contiguous(), None, scale_a.reshape(1),
+                                   scale_b.reshape(1), None, out_dtype=out_dtype)
+
+
 class ErrorFeedbackState:
     """Per-parameter state of the tensor-core path; same five dictionaries,
     keys and update rules as tcfp/core.py:298-410, so ``ef_state.pt``

@@ -13,7 +13,8 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 TOL = 1e-3
 
-SHAPES = [(128, 128, 128), (256, 384, 512), (48, 80, 112), (100, 128, 256), (1024, 1024, 1024), (130, 272, 144)]
+SHAPES = [(128, 128, 128), (256, 384, 512), (48, 80, 112), (100, 128, 256), (1024, 1024, 1024), (130, 272, 144),
+          (300, 272, 144), (1000, 528, 400), (257, 16, 16), (640, 2048, 96)]
 
 
 def _per_tensor_operands(seed, M, N, K, grad=False):
@@ -87,7 +88,8 @@ def _block_operands(seed, M, N, K, bs):
 
 
 @pytest.mark.parametrize("bs", [32, 64, 128])
-@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 384, 512), (100, 100, 256), (512, 640, 1024), (64, 192, 384)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 384, 512), (100, 100, 256), (512, 640, 1024), (64, 192, 384),
+                                   (300, 272, 384), (1000, 528, 640), (257, 16, 128)])
 def test_block_dual_gemm_forward(M, N, K, bs):
     from tcfp_b200.kernels import fused_block_scaled_dual_gemm_forward
 
@@ -115,7 +117,8 @@ def test_block_gemm_single_and_sentinel():
 
 
 @pytest.mark.parametrize("bs", [32, 64, 128])
-@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 384, 512), (100, 256, 128), (512, 1024, 640)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 384, 512), (100, 256, 128), (512, 1024, 640), (300, 384, 256),
+                                   (1000, 640, 384)])
 def test_block_backward_dx(M, N, K, bs):
     """K = D_out (contraction), N = D_in."""
     from tcfp_b200.kernels import fused_block_scaled_dual_gemm_backward_dx
@@ -144,3 +147,41 @@ def test_gemm_rejects_bad_arguments(lib):
         fused_dual_gemm_forward(a, torch.zeros(16, 32, device=DEV, dtype=torch.float8_e4m3fn), w, s, s, s)
     assert lib.tcfp_dual_gemm(None, 0, None, None, None, None, None, None, None, 0, 16, 16, 16, 0, None) == -1
     assert "NULL" in _C.last_error()
+
+
+def test_fp8_matmul_wrappers():
+    """tests/test_core.py:129-145 of the reference: relative error of the FP8 product vs the FP32 product < 0.15."""
+    from tcfp_b200.core import fp8_matmul, fp8_matmul_nn, to_fp8_e4m3
+
+    a = acts(600, 256, 512, torch.float32).to(DEV)
+    b = acts(601, 512, 384, torch.float32).to(DEV)
+    aq, sa = to_fp8_e4m3(a)
+    bq, sb = to_fp8_e4m3(b)
+    ref = a @ b
+    out = fp8_matmul(aq, bq, sa, sb)
+    assert float((out - ref).norm() / ref.norm()) < 0.15
+    deq = (aq.float() * sa) @ (bq.float() * sb)
+    assert rel_fro(out, deq) <= TOL
+    btq, sbt = to_fp8_e4m3(b.t().contiguous())
+    assert rel_fro(fp8_matmul_nn(aq, btq, sa, sbt), (aq.float() * sa) @ (btq.float() * sbt).t()) <= TOL
+
+
+def test_bf16_output_and_bias_on_pair_kernel():
+    from tcfp_b200.kernels import fused_block_scaled_dual_gemm_forward, fused_dual_gemm_backward_dx
+
+    M, N, K, bs = 512, 384, 256, 64
+    a, ea, hi, eh, lo, el = _block_operands(302, M, N, K, bs)
+    bias = torch.randn(N, generator=torch.Generator().manual_seed(1))
+    d = lambda t: t.to(DEV)
+    out = fused_block_scaled_dual_gemm_forward(d(a), d(hi), d(lo), d(ea), d(eh), d(el), bs, bias=d(bias),
+                                               out_dtype=torch.bfloat16)
+    ref = O.block_dual_gemm_nt(a, ea, hi, eh, lo, el, bs) + bias
+    assert out.dtype == torch.bfloat16 and rel_fro(out.float(), ref) <= 5e-3
+    g = acts(303, M, K, torch.float32)
+    gq, ig = O.to_fp8_e5m2(g)
+    w = weights(304, K, N, std=1.0)
+    whi, wlo, ihi, ilo, _, _, _ = O.dual_quantize_per_tensor(w)
+    out = fused_dual_gemm_backward_dx(d(gq), d(whi), d(wlo), d(ig), d(ihi), d(ilo), out_dtype=torch.bfloat16)
+    assert rel_fro(out.float(), O.dual_gemm_nn(gq, ig, whi, ihi, wlo, ilo)) <= 5e-3
+    single = fused_dual_gemm_backward_dx(d(gq), d(whi), None, d(ig), d(ihi), None)
+    assert rel_fro(single, O.dual_gemm_nn(gq, ig, whi, ihi, None, None)) <= TOL
