@@ -158,6 +158,83 @@ def _mlp_train_step_ms(world: int, dev, timed_fn) -> dict:
             "ms_per_step": ms, "parallelism": f"tp{world}" if world > 1 else "single GPU"}
 
 
+def run_train_workload(args) -> None:
+    """``--workload mlp_large`` (BASELINE.json configs[3]: MLP 4096->16384->4096, 32768 tokens, SRR, AdamW) and
+    ``--workload decoder`` (configs[4]: 4 Llama-style layers, d=4096, 32 heads, FFN 11008, 8x4096 tokens, block-64
+    EF), tensor-parallel over the launched ranks.  Prints one JSON line with the step time."""
+    import torch
+    import torch.distributed as dist
+
+    from tcfp_b200 import _C
+    from tcfp_b200.workloads import build_decoder, build_mlp
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    _C.load()
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    g = torch.Generator().manual_seed(1004)
+    if args.workload == "mlp_large":
+        d = 4096
+        model = build_mlp(d, 16384, srr=True).to(dev)
+        x = torch.randn(16 * 2048, d, generator=g).to(torch.bfloat16).to(dev)
+        desc = "MLP 4096->16384->4096 GELU, 16x2048 tokens bf16, per-tensor SRR, AdamW, fwd+bwd+step"
+        flop = 3 * 2 * 2 * x.shape[0] * d * 16384 * (5.0 / 6.0) * 2   # fwd dual + dX dual + dW single
+    else:
+        d = 4096
+        model = build_decoder().to(dev)
+        x = torch.randn(8, 4096, d, generator=g).to(torch.bfloat16).to(dev)
+        desc = "4 decoder layers d=4096 h=32 ffn=11008, batch 8 x seq 4096 bf16, block-64 EF, AdamW, fwd+bwd+step"
+        lin = 4 * (4 * d * d + 3 * d * 11008)
+        flop = 2 * x.shape[0] * x.shape[1] * lin * 5.0              # (2 fwd + 2 dX + 1 dW) products
+    target = torch.randn(x.shape, generator=g).to(torch.bfloat16).to(dev)
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-4)
+
+    def step():
+        opt.zero_grad(set_to_none=True)
+        loss = torch.nn.functional.mse_loss(model(x).float(), target.float())
+        loss.backward()
+        opt.step()
+        return loss
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clk:
+        e0.record()
+        for _ in range(args.steps):
+            loss = step()
+        e1.record()
+        barrier()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_per_step = float(ms.item()) / args.steps
+    _C.check_device_status()
+    if rank == 0:
+        print(json.dumps({
+            "metric": "train_step_ms", "value": ms_per_step, "unit": "ms", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
+            "config": {"workload": desc, "parallelism": f"tp{world}"},
+            "linear_tflops_effective": flop / (ms_per_step * 1e-3) / 1e12, "loss": float(loss.item()),
+            "clocks": clk.summary(), "peak_mem_gb": torch.cuda.max_memory_allocated() / 2**30,
+        }), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -296,8 +373,11 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="gemm", choices=["gemm", "mlp_large", "decoder"])
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.workload != "gemm" and args.impl == "ours":
+        run_train_workload(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -235,6 +235,19 @@ int32_t tcfp_bf16_dual_gemm(const void* a, const void* b_hi, const void* b_lo,
                             int64_t M, int64_t N, int64_t K, int32_t trans_b,
                             void* stream);
 
+/*
+ * Weight gradient of the block-scaled layer on the bf16 tensor-core path:
+ *     out(k_in, n_out) = x^T . (g_hi + g_lo)
+ * x (tokens, k_in) bf16 (the exactly dequantized saved activation, or the bf16
+ * input), g_hi / g_lo (tokens, n_out) the bf16 head and tail of the FP32
+ * gradient (g = g_hi + g_lo to 16 significant bits; g_lo nullable).  The
+ * result is dW TRANSPOSED.  Replaces the FP32 ``grad.t() @ activation``
+ * matmuls at tcfp/nn/__init__.py:744-750 at tensor-core speed.
+ */
+int32_t tcfp_bf16_dw_gemm(const void* x, const void* g_hi, const void* g_lo,
+                          void* out, int32_t out_dtype, int64_t tokens,
+                          int64_t k_in, int64_t n_out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -44,6 +44,7 @@ _SIGNATURES = {
     "tcfp_block_dual_gemm_static": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                               c_void_p, c_int32, c_int64, c_int64, c_int64, c_int32, c_void_p]),
     "tcfp_static_scratch_bytes_per_operand": (c_size_t, []),
+    "tcfp_bf16_dw_gemm": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_int64, c_int64, c_void_p]),
     "tcfp_bf16_dual_gemm": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_int64,
                                       c_int64, c_int32, c_void_p]),
 }

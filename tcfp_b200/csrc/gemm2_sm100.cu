@@ -581,7 +581,10 @@ int pair_gemm_dispatch(int kind, bool a_mn, bool b_mn, bool out_bf16, const void
   return out_bf16 ? launch2<KIND, BMN, true>(a, b_hi, b_lo, sf_a, sf_hi, sf_lo, out, p, stream)           \
                   : launch2<KIND, BMN, false>(a, b_hi, b_lo, sf_a, sf_hi, sf_lo, out, p, stream)
   if (a_mn) {
-    if (kind != KIND_F8 || !b_mn) return fail(TCFP_ERR_UNSUPPORTED, "pair kernel: transposed A is built for the FP8 weight gradient only");
+    if (!b_mn || kind == KIND_MXF8) return fail(TCFP_ERR_UNSUPPORTED, "pair kernel: transposed A is built for the weight gradients only");
+    if (kind == KIND_BF16)
+      return out_bf16 ? launch2<KIND_BF16, true, true, true>(a, b_hi, b_lo, sf_a, sf_hi, sf_lo, out, p, stream)
+                      : launch2<KIND_BF16, true, false, true>(a, b_hi, b_lo, sf_a, sf_hi, sf_lo, out, p, stream);
     return out_bf16 ? launch2<KIND_F8, true, true, true>(a, b_hi, b_lo, sf_a, sf_hi, sf_lo, out, p, stream)
                     : launch2<KIND_F8, true, false, true>(a, b_hi, b_lo, sf_a, sf_hi, sf_lo, out, p, stream);
   }

@@ -578,6 +578,23 @@ extern "C" int32_t tcfp_block_dual_gemm(const uint8_t* a, const uint8_t* sf_a, c
                                 : launch<KIND_MXF8, false, false>(a, w_hi, w_lo, out, p, stream);
 }
 
+extern "C" int32_t tcfp_bf16_dw_gemm(const void* x, const void* g_hi, const void* g_lo, void* out, int32_t out_dtype,
+                                     int64_t tokens, int64_t k_in, int64_t n_out, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (!x || !g_hi || !out) return fail(TCFP_ERR_INVALID, "bf16_dw_gemm: NULL pointer");
+  if (out_dtype != TCFP_F32 && out_dtype != TCFP_BF16) return fail(TCFP_ERR_INVALID, "bf16_dw_gemm: output must be float32 or bfloat16");
+  int rc = check_dims("bf16_dw_gemm", k_in, n_out, tokens);
+  if (rc != TCFP_OK) return rc;
+  const bool obf = out_dtype == TCFP_BF16;
+  if (use_pair_kernel(k_in))
+    return pair_gemm_dispatch(KIND_BF16, true, true, obf, x, g_hi, g_lo, nullptr, nullptr, nullptr, out, (int)k_in,
+                              (int)n_out, (int)tokens, 0, 0, nullptr, nullptr, nullptr, nullptr, stream);
+  GemmParams p{};
+  p.M = (int)k_in; p.N = (int)n_out; p.K = (int)tokens;
+  return obf ? launch<KIND_BF16, true, true, true>(x, g_hi, g_lo, out, p, stream)
+             : launch<KIND_BF16, true, false, true>(x, g_hi, g_lo, out, p, stream);
+}
+
 extern "C" int32_t tcfp_bf16_dual_gemm(const void* a, const void* b_hi, const void* b_lo, const float* bias, void* out,
                                        int32_t out_dtype, int64_t M, int64_t N, int64_t K, int32_t trans_b,
                                        void* stream_) {

@@ -128,6 +128,26 @@ def fp8_weight_grad(grad_fp8, act_fp8, grad_inv, act_inv, *, out_dtype=torch.flo
     return out
 
 
+def bf16_weight_grad(grad: torch.Tensor, act_bf16: torch.Tensor) -> torch.Tensor:
+    """``dW = grad^T @ act`` -> ``(D_out, D_in)`` FP32 for an FP32 (or bf16)
+    gradient ``(M, D_out)`` and a bf16 activation ``(M, D_in)``: the gradient
+    is split into a bf16 head and tail (16 significant bits) and both ride one
+    bf16 tensor-core GEMM -- the FP32 matmul of tcfp/nn/__init__.py:744-750 at
+    about a tenth of its time.  Returns a transposed view (the kernel produces
+    dW^T)."""
+    M, D_out = grad.shape
+    M2, D_in = act_bf16.shape
+    assert M == M2 and act_bf16.dtype == torch.bfloat16
+    g_hi = grad.to(torch.bfloat16)
+    g_lo = None
+    if grad.dtype == torch.float32:
+        g_lo = (grad - g_hi.float()).to(torch.bfloat16)
+    out = torch.empty((D_in, D_out), device=grad.device, dtype=torch.float32)
+    _C.check(_C.load().tcfp_bf16_dw_gemm(_C.ptr(act_bf16.contiguous()), _C.ptr(g_hi), _C.ptr(g_lo), _C.ptr(out),
+                                         _C.F32, M, D_in, D_out, _C.stream()))
+    return out.t()
+
+
 # ---------------------------------------------------------------------------
 # block quantizers (tcfp/kernels.py:1675-1875)
 # ---------------------------------------------------------------------------

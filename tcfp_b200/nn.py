@@ -34,6 +34,8 @@ from .kernels import (
     fused_dual_gemm_backward_dx,
     fused_dual_gemm_forward,
     fused_dual_quantize_fp8,
+    bf16_weight_grad,
+    block_dequantize_bf16,
     fp8_weight_grad,
 )
 
@@ -112,7 +114,10 @@ class _TCFP12TensorCoreFunction(torch.autograd.Function):
         grad_input = fused_dual_gemm_backward_dx(grad_fp8, w_hi, w_lo, grad_inv, inv_hi, inv_lo)
         grad_input = grad_input.reshape(ctx.input_shape)
         if ctx.hp_grad_weight:
-            grad_weight = g2d.float().t() @ saved_act.float()    # (:541-542)
+            if saved_act.dtype == torch.bfloat16 and g2d.shape[1] % 16 == 0 and saved_act.shape[1] % 16 == 0:
+                grad_weight = bf16_weight_grad(g2d, saved_act)
+            else:
+                grad_weight = g2d.float().t() @ saved_act.float()    # (:541-542)
         else:
             grad_weight = fp8_weight_grad(grad_fp8, saved_act, grad_inv, act_inv)   # (:546-555)
         grad_bias = g2d.float().sum(dim=0) if ctx.has_bias else None
@@ -183,9 +188,13 @@ class _TCFP12BlockScaledFunction(torch.autograd.Function):
                                                     grad_bf16=grad_bf16).reshape(ctx.input_shape)
         # dW in full precision, as in the reference (:744-750)
         if ctx.hp_grad_weight:
-            grad_weight = g2d.float().t() @ saved_act.float()
+            if saved_act.dtype == torch.bfloat16:
+                grad_weight = bf16_weight_grad(g2d, saved_act)
+            else:
+                grad_weight = g2d.float().t() @ saved_act.float()
         else:
-            grad_weight = g2d.float().t() @ block_dequantize_fp8(saved_act, act_scales, bs)
+            # the saved codes dequantize exactly to bf16; the FP32 gradient goes in as bf16 head + tail
+            grad_weight = bf16_weight_grad(g2d, block_dequantize_bf16(saved_act, act_scales, bs))
         grad_bias = g2d.float().sum(dim=0) if ctx.has_bias else None
         return (grad_input, grad_weight, grad_bias) + (None,) * 9
 

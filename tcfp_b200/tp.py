@@ -79,9 +79,13 @@ class ColumnParallelLinear(nn.Module):
     """``y_local = x @ W[rows of this rank].T``; output stays sharded."""
 
     def __init__(self, in_features: int, out_features: int, bias: bool = True, *, group=None, granule: int = 16,
-                 layer_factory: Callable[..., nn.Module] = _default_factory, **layer_kw):
+                 layer_factory: Callable[..., nn.Module] = _default_factory, reduce_input_grad: bool = True,
+                 **layer_kw):
         super().__init__()
         self.group = group
+        # several column-parallel layers fed by one tensor (q/k/v, gate/up) share a single
+        # gradient all-reduce: the caller applies copy_to_parallel once and turns this off
+        self.reduce_input_grad = reduce_input_grad
         world = dist.get_world_size(group) if dist.is_initialized() else 1
         rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.out_start, self.out_end = shard_bounds(out_features, world, rank, granule)
@@ -89,7 +93,14 @@ class ColumnParallelLinear(nn.Module):
         self.inner = layer_factory(in_features, self.out_end - self.out_start, bias, **layer_kw)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.inner(_CopyToParallel.apply(x, self.group))
+        if self.reduce_input_grad:
+            x = _CopyToParallel.apply(x, self.group)
+        return self.inner(x)
+
+
+def copy_to_parallel(x: torch.Tensor, group=None) -> torch.Tensor:
+    """Identity forward, gradient all-reduce backward."""
+    return _CopyToParallel.apply(x, group)
 
 
 class RowParallelLinear(nn.Module):

@@ -205,3 +205,15 @@ def test_host_streamed_linear_matches_unchunked():
         # instead of in the accumulator: same products, different FP32 summation order
         assert rel_fro(out_host, want) <= 1e-5
         assert torch.equal(lin.err, err)
+
+
+def test_bf16_weight_grad_is_fp32_accurate():
+    from tcfp_b200.kernels import bf16_weight_grad
+
+    for M, N, K in [(512, 256, 384), (1000, 128, 512), (300, 320, 96)]:
+        g = acts(60, M, N, torch.float32) * 0.01
+        x = acts(61, M, K, torch.bfloat16)
+        ref = g.double().t() @ x.double()
+        out = bf16_weight_grad(g.to(DEV), x.to(DEV))
+        assert out.shape == (N, K)
+        assert rel_fro(out, ref) <= 2e-5
