@@ -138,6 +138,12 @@ def bf16_weight_grad(grad: torch.Tensor, act_bf16: torch.Tensor) -> torch.Tensor
     M, D_out = grad.shape
     M2, D_in = act_bf16.shape
     assert M == M2 and act_bf16.dtype == torch.bfloat16
+    if grad.dtype == torch.bfloat16:
+        # nothing to split: compute dW = grad^T @ act directly (grad is the transposed operand)
+        out = torch.empty((D_out, D_in), device=grad.device, dtype=torch.float32)
+        _C.check(_C.load().tcfp_bf16_dw_gemm(_C.ptr(grad.contiguous()), _C.ptr(act_bf16.contiguous()), None, _C.ptr(out),
+                                             _C.F32, M, D_out, D_in, _C.stream()))
+        return out
     g_hi = grad.to(torch.bfloat16)
     g_lo = None
     if grad.dtype == torch.float32:

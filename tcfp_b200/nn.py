@@ -44,6 +44,12 @@ def _flat2d(t: torch.Tensor) -> torch.Tensor:
     return t.reshape(-1, t.shape[-1]).contiguous()
 
 
+def _dx_dtype(input: torch.Tensor) -> torch.dtype:
+    # autograd casts the input gradient to the input's dtype anyway; a bf16 input gets its gradient
+    # written as bf16 by the GEMM epilogue instead of an FP32 tensor plus a conversion pass
+    return torch.bfloat16 if input.dtype == torch.bfloat16 else torch.float32
+
+
 def _master(weight: torch.Tensor) -> torch.Tensor:
     w = weight.detach()
     if w.dtype not in (torch.float32, torch.bfloat16):
@@ -60,7 +66,7 @@ class _TCFP12TensorCoreFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, input, weight, bias, hp_grad_weight, error_state, param_name, delayed_scaling, abd, srr,
-                update_ef, srr_seed, srr_offset):
+                update_ef, srr_seed, srr_offset, out_dtype=torch.float32):
         w = _master(weight)
         error_buf = None
         if error_state is not None:
@@ -87,7 +93,9 @@ class _TCFP12TensorCoreFunction(torch.autograd.Function):
         x2d = _flat2d(input)
         act_fp8, act_inv = to_fp8_e4m3(x2d)                      # always fresh (:390)
         out2d = fused_dual_gemm_forward(act_fp8, w_hi, w_lo, act_inv, inv_hi, inv_lo,
-                                        bias=None if bias is None else bias.detach().float().contiguous())
+                                        bias=None if bias is None else bias.detach().float().contiguous(),
+                                        out_dtype=out_dtype)
+        ctx.dx_dtype = _dx_dtype(input)
         ctx.hp_grad_weight = hp_grad_weight
         ctx.input_shape = input_shape
         ctx.has_bias = bias is not None
@@ -111,7 +119,8 @@ class _TCFP12TensorCoreFunction(torch.autograd.Function):
         if g2d.dtype not in (torch.float32, torch.bfloat16):
             g2d = g2d.float()
         grad_fp8, grad_inv = to_fp8_e5m2(g2d)                    # always fresh (:494)
-        grad_input = fused_dual_gemm_backward_dx(grad_fp8, w_hi, w_lo, grad_inv, inv_hi, inv_lo)
+        grad_input = fused_dual_gemm_backward_dx(grad_fp8, w_hi, w_lo, grad_inv, inv_hi, inv_lo,
+                                                 out_dtype=ctx.dx_dtype)
         grad_input = grad_input.reshape(ctx.input_shape)
         if ctx.hp_grad_weight:
             if saved_act.dtype == torch.bfloat16 and g2d.shape[1] % 16 == 0 and saved_act.shape[1] % 16 == 0:
@@ -121,7 +130,7 @@ class _TCFP12TensorCoreFunction(torch.autograd.Function):
         else:
             grad_weight = fp8_weight_grad(grad_fp8, saved_act, grad_inv, act_inv)   # (:546-555)
         grad_bias = g2d.float().sum(dim=0) if ctx.has_bias else None
-        return (grad_input, grad_weight, grad_bias) + (None,) * 9
+        return (grad_input, grad_weight, grad_bias) + (None,) * 10
 
 
 # ---------------------------------------------------------------------------
@@ -133,7 +142,7 @@ class _TCFP12BlockScaledFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, input, weight, bias, scale_block_size, hp_grad_weight, error_state, param_name, abd, srr,
-                update_ef, srr_seed, srr_offset):
+                update_ef, srr_seed, srr_offset, out_dtype=torch.float32):
         w = _master(weight)
         error_buf = None
         if error_state is not None:
@@ -151,7 +160,8 @@ class _TCFP12BlockScaledFunction(torch.autograd.Function):
         act_fp8, act_scales = block_quantize_fp8(x2d, bs, torch.float8_e4m3fn)
         out2d = fused_block_scaled_dual_gemm_forward(
             act_fp8, w_hi, w_lo, act_scales, s_hi, s_lo, bs,
-            bias=None if bias is None else bias.detach().float().contiguous())
+            bias=None if bias is None else bias.detach().float().contiguous(), out_dtype=out_dtype)
+        ctx.dx_dtype = _dx_dtype(input)
         ctx.hp_grad_weight = hp_grad_weight
         ctx.input_shape = input_shape
         ctx.has_bias = bias is not None
@@ -185,7 +195,7 @@ class _TCFP12BlockScaledFunction(torch.autograd.Function):
         # pass emits the dequantized bf16 copy the dX GEMM consumes
         grad_fp8, grad_scales, grad_bf16 = block_quantize_fp8(g2d, bs, torch.float8_e5m2, want_bf16=True)
         grad_input = fused_block_scaled_backward_dx(grad_fp8, w_hi, w_lo, grad_scales, s_hi, s_lo, bs,
-                                                    grad_bf16=grad_bf16).reshape(ctx.input_shape)
+                                                    grad_bf16=grad_bf16, out_dtype=ctx.dx_dtype).reshape(ctx.input_shape)
         # dW in full precision, as in the reference (:744-750)
         if ctx.hp_grad_weight:
             if saved_act.dtype == torch.bfloat16:
@@ -196,7 +206,7 @@ class _TCFP12BlockScaledFunction(torch.autograd.Function):
             # the saved codes dequantize exactly to bf16; the FP32 gradient goes in as bf16 head + tail
             grad_weight = bf16_weight_grad(g2d, block_dequantize_bf16(saved_act, act_scales, bs))
         grad_bias = g2d.float().sum(dim=0) if ctx.has_bias else None
-        return (grad_input, grad_weight, grad_bias) + (None,) * 9
+        return (grad_input, grad_weight, grad_bias) + (None,) * 10
 
 
 # ---------------------------------------------------------------------------
@@ -210,9 +220,10 @@ class TCFPLinear(nn.Module):
     tcfp/nn/__init__.py:810-946; flags are re-read on every forward because
     training policies mutate them live.  ``use_fused_kernel`` and
     ``use_cuda_ext`` are accepted for compatibility: there is exactly one
-    backend here.  Additional keyword ``srr_seed`` seeds the stochastic
+    backend here.  Additional keywords: ``srr_seed`` seeds the stochastic
     residual stream (element ``n*K+k`` of forward call ``i`` draws
-    ``philox(seed, i*N*K + n*K + k)``).
+    ``philox(seed, i*N*K + n*K + k)``); ``out_dtype=torch.bfloat16`` makes the
+    GEMM epilogue write bf16 (the reference always returns FP32).
     """
 
     def __init__(self, in_features: int, out_features: int, bias: bool = True, mode: TCFPMode = TCFPMode.TCFP12,
@@ -221,7 +232,7 @@ class TCFPLinear(nn.Module):
                  use_tensor_cores: bool = False, hp_grad_weight: bool = False, error_feedback: bool = True,
                  delayed_scaling: bool = False, use_fused_kernel: bool = True, use_cuda_ext: bool = True,
                  scale_block_size: int | None = None, abd: bool = False, srr: bool = False,
-                 srr_seed: int | None = None, device=None, dtype=None) -> None:
+                 srr_seed: int | None = None, out_dtype: torch.dtype = torch.float32, device=None, dtype=None) -> None:
         super().__init__()
         if nf4_residual and use_tensor_cores and mode == TCFPMode.TCFP12:
             warnings.warn("nf4_residual is ignored in tensor core mode — NF4 cannot run on tensor cores. "
@@ -277,6 +288,9 @@ class TCFPLinear(nn.Module):
             delayed_scaling = False
             self.delayed_scaling = False
         self.srr = srr
+        if out_dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError("out_dtype must be torch.float32 (the reference's output type) or torch.bfloat16")
+        self.out_dtype = out_dtype
         self.srr_seed = int(srr_seed if srr_seed is not None else (torch.initial_seed() & 0x7FFFFFFF))
         self._srr_offset = 0
 
@@ -335,10 +349,10 @@ class TCFPLinear(nn.Module):
         if self.mode == TCFPMode.TCFP12 and self.scale_block_size is not None:
             return _TCFP12BlockScaledFunction.apply(
                 x, self.weight, self.bias, self.scale_block_size, self.hp_grad_weight, self._error_state,
-                self._param_name, self.abd, srr, update_ef, self.srr_seed, srr_offset)
+                self._param_name, self.abd, srr, update_ef, self.srr_seed, srr_offset, self.out_dtype)
         return _TCFP12TensorCoreFunction.apply(
             x, self.weight, self.bias, self.hp_grad_weight, self._error_state, self._param_name,
-            self.delayed_scaling, self.abd, srr, update_ef, self.srr_seed, srr_offset)
+            self.delayed_scaling, self.abd, srr, update_ef, self.srr_seed, srr_offset, self.out_dtype)
 
     def extra_repr(self) -> str:
         parts = [f"in_features={self.in_features}", f"out_features={self.out_features}",

@@ -56,19 +56,19 @@ class DecoderLayer(nn.Module):
         B, T, _ = x.shape
         h = copy_to_parallel(self.norm1(x))
         shp = (B, T, self.heads_local, self.head_dim)
-        q = self.q(h).to(torch.bfloat16).view(shp).transpose(1, 2)
-        k = self.k(h).to(torch.bfloat16).view(shp).transpose(1, 2)
-        v = self.v(h).to(torch.bfloat16).view(shp).transpose(1, 2)
+        q = self.q(h).view(shp).transpose(1, 2)
+        k = self.k(h).view(shp).transpose(1, 2)
+        v = self.v(h).view(shp).transpose(1, 2)
         a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
         a = a.transpose(1, 2).reshape(B, T, self.heads_local * self.head_dim)
-        x = x + self.o(a).to(x.dtype)
+        x = x + self.o(a)
         h = copy_to_parallel(self.norm2(x))
-        f = (F.silu(self.gate(h)) * self.up(h)).to(torch.bfloat16)
-        return x + self.down(f).to(x.dtype)
+        f = F.silu(self.gate(h)) * self.up(h)
+        return x + self.down(f)
 
 
 def build_decoder(n_layers=4, d_model=4096, n_heads=32, ffn=11008, block=64, **layer_kw) -> nn.Module:
-    kw = dict(scale_block_size=block, **layer_kw)
+    kw = dict(scale_block_size=block, out_dtype=torch.bfloat16, **layer_kw)
     m = nn.Sequential(*[DecoderLayer(d_model, n_heads, ffn, granule=block, **kw) for _ in range(n_layers)])
     _name_layers(m)
     _init_weights(m)

@@ -217,3 +217,25 @@ def test_bf16_weight_grad_is_fp32_accurate():
         out = bf16_weight_grad(g.to(DEV), x.to(DEV))
         assert out.shape == (N, K)
         assert rel_fro(out, ref) <= 2e-5
+
+
+def test_bf16_weight_grad_bf16_gradient_and_bf16_layer_output():
+    from tcfp_b200.kernels import bf16_weight_grad
+    from tcfp_b200.nn import TCFPLinear
+
+    g = acts(62, 640, 256, torch.bfloat16)
+    x = acts(63, 640, 384, torch.bfloat16)
+    out = bf16_weight_grad(g.to(DEV), x.to(DEV))
+    assert out.is_contiguous() and rel_fro(out, g.double().t() @ x.double()) <= 2e-5
+    layer = TCFPLinear(384, 256, use_tensor_cores=True, scale_block_size=64, out_dtype=torch.bfloat16).to(DEV)
+    xin = x.to(DEV).requires_grad_(True)
+    y = layer(xin)
+    assert y.dtype == torch.bfloat16
+    y.backward(g.to(DEV))
+    assert xin.grad.dtype == torch.bfloat16 and layer.weight.grad.dtype == torch.float32
+    ref = TCFPLinear(384, 256, use_tensor_cores=True, scale_block_size=64).to(DEV)
+    ref.load_state_dict(layer.state_dict())
+    x2 = x.to(DEV).requires_grad_(True)
+    y2 = ref(x2)
+    y2.backward(g.to(DEV).float())
+    assert rel_fro(y.float(), y2) <= 5e-3 and rel_fro(layer.weight.grad, ref.weight.grad) <= 1e-3
