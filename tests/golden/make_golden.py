@@ -113,6 +113,20 @@ for name, cfg in LAYER_CASES.items():
                 layer.weight -= 0.05 * layer.weight.grad      # plain SGD keeps the fixture self-contained
     finally:
         rcore.torch.rand_like = orig
+    if name == "delayed":
+        layer_for_ckpt = layer
+
+# ef_state.pt as the reference's own checkpointer writes it, for the delayed-scaling layer after two steps
+import tempfile  # noqa: E402
+
+from tcfp.training.checkpointing import TCFPCheckpointer  # noqa: E402
+
+wrap = torch.nn.Sequential()
+wrap.add_module("layer", layer_for_ckpt)
+with tempfile.TemporaryDirectory() as td:
+    ck = TCFPCheckpointer(td)
+    ck._save_ef_state(Path(td), wrap)
+    (HERE / "ef_state_ref.pt").write_bytes((Path(td) / "ef_state.pt").read_bytes())
 
 np.savez_compressed(HERE / "per_tensor.npz", **out)
 print("wrote", HERE / "per_tensor.npz", len(out), "arrays",

@@ -1,0 +1,102 @@
+"""CPU: ``ErrorFeedbackState`` state machine (the reference's
+tests/test_delayed_scaling.py:22-118 run on CPU tensors) and the ``ef_state.pt``
+schema, including a file written by the reference's own checkpointer."""
+from pathlib import Path
+
+import numpy as np
+import torch
+
+from tcfp_b200.checkpoint import ef_state_dict, load_ef_state, save_ef_state
+from tcfp_b200.core import ErrorFeedbackState
+from tcfp_b200.nn import TCFPLinear, convert_to_tcfp
+
+GOLD = Path(__file__).parent / "golden"
+
+
+def test_delayed_amax_first_call_and_ema():
+    st = ErrorFeedbackState()
+    a = torch.tensor(3.14)
+    assert torch.allclose(st.get_delayed_amax("w", a), a)
+    st = ErrorFeedbackState()
+    st.get_delayed_amax("w", torch.tensor(1.0))
+    for _ in range(5000):
+        r = st.get_delayed_amax("w", torch.tensor(2.0))
+    assert abs(r.item() - 2.0) < 0.1
+    st = ErrorFeedbackState()
+    for _ in range(101):
+        st.get_delayed_amax("w", torch.tensor(1.0))
+    assert st.get_delayed_amax("w", torch.tensor(10.0)).item() < 2.0       # one spike is smoothed
+
+
+def test_residual_prediction_and_validation_cadence():
+    st = ErrorFeedbackState()
+    main = torch.tensor(4.0)
+    assert torch.allclose(st.predict_residual_amax("w", main), torch.tensor(0.5))     # amax / 8 fallback
+    st.update_residual_ratio("w", main, torch.tensor(0.8))
+    assert abs(st.predict_residual_amax("w", main).item() - 0.8) < 0.01
+    st = ErrorFeedbackState(residual_validation_interval=10)
+    res = [st.should_validate_residual("w") for _ in range(25)]
+    assert res[0] and res[9] and res[19] and not res[1] and not res[5]
+    st.get_delayed_amax("w", torch.tensor(1.0))
+    st.reset()
+    assert st.should_validate_residual("w") is True and not st._delayed_amax and not st._buffers
+
+
+def test_error_buffer_is_lazy_fp32_and_rebinds():
+    st = ErrorFeedbackState()
+    like = torch.zeros(4, 8, dtype=torch.bfloat16)
+    buf = st.get_error("p", like)
+    assert buf.dtype == torch.float32 and buf.shape == (4, 8) and st.get_error("p", like) is buf
+    assert st.get_error("p", torch.zeros(2, 8)).shape == (2, 8)          # shape change re-allocates
+    new = torch.ones(2, 8)
+    st.update_error("p", new)
+    assert st._buffers["p"].data_ptr() == new.data_ptr()        # detached alias, no copy
+
+
+def test_ef_state_schema_round_trip(tmp_path):
+    model = torch.nn.Sequential(torch.nn.Linear(32, 64), torch.nn.ReLU(), torch.nn.Linear(64, 32))
+    convert_to_tcfp(model, skip_patterns=(), delayed_scaling=True)
+    l0 = model[0]
+    assert isinstance(l0, TCFPLinear) and l0._param_name == "0"
+    st = l0._error_state
+    st._buffers["0"] = torch.randn(64, 32)
+    st._delayed_amax["0.w_hi"] = torch.tensor(0.3)
+    st._residual_ratio["0.ratio"] = torch.tensor(0.11)
+    st._step_count["0.steps"] = 7
+    snap = ef_state_dict(model)
+    assert set(snap) == {"0", "2"}
+    assert set(snap["0"]) == {"_buffers", "_amax_ema", "_delayed_amax", "_residual_ratio", "_step_count", "_ema_decay"}
+    save_ef_state(model, tmp_path / "ef_state.pt")
+    fresh = torch.nn.Sequential(torch.nn.Linear(32, 64), torch.nn.ReLU(), torch.nn.Linear(64, 32))
+    convert_to_tcfp(fresh, skip_patterns=(), delayed_scaling=True)
+    load_ef_state(fresh, tmp_path / "ef_state.pt")
+    f = fresh[0]._error_state
+    assert torch.equal(f._buffers["0"], st._buffers["0"]) and f._step_count["0.steps"] == 7
+    assert torch.equal(f._delayed_amax["0.w_hi"], torch.tensor(0.3))
+    assert torch.equal(f._residual_ratio["0.ratio"], torch.tensor(0.11))
+
+
+def test_loads_a_file_written_by_the_reference_checkpointer():
+    """``ef_state_ref.pt`` was written by the reference's TCFPCheckpointer for
+    the delayed-scaling golden layer after its two steps."""
+    gold = np.load(GOLD / "per_tensor.npz")
+    wrap = torch.nn.Sequential()
+    layer = TCFPLinear(64, 48, use_tensor_cores=True, delayed_scaling=True)
+    layer._param_name = "layer"
+    wrap.add_module("layer", layer)
+    load_ef_state(wrap, GOLD / "ef_state_ref.pt")
+    st = layer._error_state
+    bits = lambda t: t.float().contiguous().view(torch.int32).numpy()  # noqa: E731
+    assert np.array_equal(bits(st._buffers["layer"]), gold["layer/delayed/step1/ef"])
+    assert np.array_equal(bits(st._delayed_amax["layer.w_hi"].reshape(1)), gold["layer/delayed/step1/delayed/layer.w_hi"])
+    assert np.array_equal(bits(st._residual_ratio["layer.ratio"].reshape(1)), gold["layer/delayed/step1/ratio/layer.ratio"])
+    assert st._step_count["layer.steps"] == 2
+
+
+def test_srr_stream_position_is_checkpointed(tmp_path):
+    m = torch.nn.Sequential(TCFPLinear(32, 32, use_tensor_cores=True, srr=True, srr_seed=5))
+    m[0]._srr_offset = 4096
+    save_ef_state(m, tmp_path / "s.pt")
+    n = torch.nn.Sequential(TCFPLinear(32, 32, use_tensor_cores=True, srr=True, srr_seed=9))
+    load_ef_state(n, tmp_path / "s.pt")
+    assert n[0].srr_seed == 5 and n[0]._srr_offset == 4096
