@@ -154,8 +154,31 @@ def _mlp_train_step_ms(world: int, dev, timed_fn) -> dict:
 
     steps = 10
     ms = timed_fn(step, steps, 3) / steps
-    return {"config": "MLP 1024->4096->1024 GELU, 8192 tokens bf16, per-tensor EF, Adam, fwd+bwd+step",
-            "ms_per_step": ms, "parallelism": f"tp{world}" if world > 1 else "single GPU"}
+    res = {"config": "MLP 1024->4096->1024 GELU, 8192 tokens bf16, per-tensor EF, Adam, fwd+bwd+step",
+           "ms_per_step": ms, "parallelism": f"tp{world}" if world > 1 else "single GPU"}
+    if world == 1:
+        # the same step captured once in a CUDA graph and replayed: ~45 launches lose their launch gaps
+        try:
+            opt_g = torch.optim.Adam(model.parameters(), lr=1e-4, capturable=True)
+
+            def gstep():
+                opt_g.zero_grad(set_to_none=False)
+                torch.nn.functional.mse_loss(model(x), target).backward()
+                opt_g.step()
+
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(3):
+                    gstep()
+            torch.cuda.current_stream().wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                gstep()
+            res["ms_per_step_cuda_graph"] = timed_fn(graph.replay, steps, 3) / steps
+        except Exception as e:
+            res["cuda_graph_error"] = repr(e)[:160]
+    return res
 
 
 def run_train_workload(args) -> None:

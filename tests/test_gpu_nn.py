@@ -239,3 +239,44 @@ def test_bf16_weight_grad_bf16_gradient_and_bf16_layer_output():
     y2 = ref(x2)
     y2.backward(g.to(DEV).float())
     assert rel_fro(y.float(), y2) <= 5e-3 and rel_fro(layer.weight.grad, ref.weight.grad) <= 1e-3
+
+
+@pytest.mark.parametrize("kw", [dict(scale_block_size=64), dict()])
+def test_layer_step_replays_from_a_cuda_graph(kw):
+    """Forward + backward of a layer captured once and replayed: every launch
+    of the library (memsets, quantizers, TMA-descriptor GEMMs) is capturable
+    after one eager warm-up, and a replay reproduces the eager step."""
+    from tcfp_b200.nn import TCFPLinear
+
+    torch.manual_seed(3)
+    layer = TCFPLinear(256, 384, use_tensor_cores=True, error_feedback=False, **kw).to(DEV)
+    x = acts(70, 512, 256, torch.bfloat16).to(DEV).requires_grad_(True)
+    g = acts(71, 512, 384, torch.float32).to(DEV)
+
+    def step():
+        layer.weight.grad = None
+        x.grad = None
+        y = layer(x)
+        y.backward(g)
+        return y
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            y_eager = step().detach().clone()
+    torch.cuda.current_stream().wait_stream(side)
+    dw_eager, dx_eager = layer.weight.grad.clone(), x.grad.clone()
+
+    graph = torch.cuda.CUDAGraph()
+    layer.weight.grad = None
+    x.grad = None
+    with torch.cuda.graph(graph):
+        y_static = layer(x)
+        y_static.backward(g)
+    dw_static, dx_static = layer.weight.grad, x.grad
+    for _ in range(2):
+        graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(y_static, y_eager)
+    assert torch.equal(dw_static, dw_eager) and torch.equal(dx_static, dx_eager)
