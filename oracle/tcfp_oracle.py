@@ -137,6 +137,13 @@ def to_fp8_e4m3_sr(t: torch.Tensor, rand: torch.Tensor, scale: torch.Tensor | No
     return stochastic_round_to_fp8_e4m3(scaled, rand), inv
 
 
+def nf_aware_target_max(t: torch.Tensor, sigma_factor: float = 3.0) -> torch.Tensor:
+    """tcfp/core.py:182-185."""
+    t = t.float()
+    std = t.std().clamp(min=1e-12)
+    return t.abs().max().clamp(min=1e-12) if std < 1e-6 else sigma_factor * std
+
+
 def dual_quantize_per_tensor(
     weight: torch.Tensor,
     error: torch.Tensor | None = None,

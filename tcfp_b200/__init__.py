@@ -14,6 +14,7 @@ from .core import (  # noqa: F401
     fp8_matmul,
     fp8_matmul_nn,
     to_fp8_e4m3,
+    to_fp8_e4m3_nf_aware,
     to_fp8_e4m3_sr,
     to_fp8_e5m2,
 )

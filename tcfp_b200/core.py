@@ -67,6 +67,25 @@ def to_fp8_e5m2(tensor: torch.Tensor, scale: torch.Tensor | None = None):
     return _cast(tensor, scale, torch.float8_e5m2, _C.E5M2, "to_fp8_e5m2")
 
 
+def nf_aware_target_max(tensor: torch.Tensor, sigma_factor: float = 3.0) -> torch.Tensor:
+    """The effective maximum of tcfp/core.py:182-185: ``sigma_factor * std``,
+    or the amax for near-constant tensors (std < 1e-6).  The standard
+    deviation is torch's own reduction, as in the reference."""
+    t = tensor.float()
+    std = t.std().clamp(min=1e-12)
+    return torch.where(std < 1e-6, t.abs().max().clamp(min=1e-12), sigma_factor * std)
+
+
+def to_fp8_e4m3_nf_aware(tensor: torch.Tensor, sigma_factor: float = 3.0, stochastic: bool = False, *,
+                         seed: int = 0, offset: int = 0):
+    """tcfp/core.py:161-193: scale to ``sigma_factor`` standard deviations
+    instead of the maximum; values beyond are clipped to +-448."""
+    scale = (FP8_E4M3_MAX / nf_aware_target_max(tensor, sigma_factor)).to(torch.float32)
+    if stochastic:
+        return to_fp8_e4m3_sr(tensor, scale, seed=seed, offset=offset)
+    return to_fp8_e4m3(tensor, scale)
+
+
 def absmax(tensor: torch.Tensor, error: torch.Tensor | None = None) -> torch.Tensor:
     """``max |tensor (+ error)|`` as a 0-dim float32 device tensor
     (the reduction of tcfp/core.py:100, tcfp/nn/__init__.py:282)."""

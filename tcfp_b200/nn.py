@@ -23,6 +23,7 @@ from .core import (
     TCFPMode,
     absmax,
     dual_quantize_per_tensor,
+    nf_aware_target_max,
     to_fp8_e4m3,
     to_fp8_e5m2,
 )
@@ -66,14 +67,31 @@ class _TCFP12TensorCoreFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, input, weight, bias, hp_grad_weight, error_state, param_name, delayed_scaling, abd, srr,
-                update_ef, srr_seed, srr_offset, out_dtype=torch.float32):
+                update_ef, srr_seed, srr_offset, out_dtype=torch.float32, nf_sigma=None):
         w = _master(weight)
         error_buf = None
         if error_state is not None:
             # lazily zero-initialised FP32 buffer, updated in place by the kernel
             error_buf = error_state.get_error(param_name, w)
 
-        if delayed_scaling and error_state is not None:
+        if nf_sigma is not None:
+            # sigma-based scale for W_hi (tcfp/nn/__init__.py:356-359, tcfp/core.py:161-193); with delayed
+            # scaling the sigma target feeds the EMA instead of the amax (:263-280)
+            target = nf_aware_target_max(w.float() + error_buf if error_buf is not None else w, nf_sigma)
+            if delayed_scaling and error_state is not None:
+                target = error_state.get_delayed_amax(param_name + ".w_hi", target)
+                if error_state.should_validate_residual(param_name):
+                    w_hi, w_lo, inv_hi, inv_lo, amax = dual_quantize_per_tensor(
+                        w, error_buf, update_error=update_ef, amax_hi=target, want_amax=True)
+                    error_state.update_residual_ratio(param_name, target, amax[1].clamp(min=1e-12))
+                else:
+                    w_hi, w_lo, inv_hi, inv_lo, _ = dual_quantize_per_tensor(
+                        w, error_buf, update_error=update_ef, amax_hi=target,
+                        amax_lo=error_state.predict_residual_amax(param_name, target))
+            else:
+                w_hi, w_lo, inv_hi, inv_lo, _ = dual_quantize_per_tensor(
+                    w, error_buf, srr=srr, update_error=update_ef, seed=srr_seed, offset=srr_offset, amax_hi=target)
+        elif delayed_scaling and error_state is not None:
             # predictive dual-track delayed scaling (tcfp/nn/__init__.py:250-309)
             current = absmax(w, error_buf).clamp(min=1e-12)
             delayed = error_state.get_delayed_amax(param_name + ".w_hi", current)
@@ -130,7 +148,7 @@ class _TCFP12TensorCoreFunction(torch.autograd.Function):
         else:
             grad_weight = fp8_weight_grad(grad_fp8, saved_act, grad_inv, act_inv)   # (:546-555)
         grad_bias = g2d.float().sum(dim=0) if ctx.has_bias else None
-        return (grad_input, grad_weight, grad_bias) + (None,) * 10
+        return (grad_input, grad_weight, grad_bias) + (None,) * 11
 
 
 # ---------------------------------------------------------------------------
@@ -239,8 +257,8 @@ class TCFPLinear(nn.Module):
                           "The residual uses FP8 E4M3 instead.", stacklevel=2)
         if delayed_scaling and not use_tensor_cores:
             warnings.warn("delayed_scaling requires use_tensor_cores=True and is ignored without it.", stacklevel=2)
-        if nf_aware_scaling and use_tensor_cores:
-            raise ValueError("nf_aware_scaling (sigma-based scales) is not provided on the tensor-core path of this build")
+        if nf_aware_scaling and stochastic_rounding and use_tensor_cores:
+            raise ValueError("nf_aware_scaling with stochastic_rounding of W_hi is not provided on the tensor-core path")
         self.in_features = in_features
         self.out_features = out_features
         self.mode = mode
@@ -352,7 +370,8 @@ class TCFPLinear(nn.Module):
                 self._param_name, self.abd, srr, update_ef, self.srr_seed, srr_offset, self.out_dtype)
         return _TCFP12TensorCoreFunction.apply(
             x, self.weight, self.bias, self.hp_grad_weight, self._error_state, self._param_name,
-            self.delayed_scaling, self.abd, srr, update_ef, self.srr_seed, srr_offset, self.out_dtype)
+            self.delayed_scaling, self.abd, srr, update_ef, self.srr_seed, srr_offset, self.out_dtype,
+            self.sigma_factor if self.nf_aware_scaling else None)
 
     def extra_repr(self) -> str:
         parts = [f"in_features={self.in_features}", f"out_features={self.out_features}",
@@ -361,6 +380,8 @@ class TCFPLinear(nn.Module):
             parts.append("use_tensor_cores=True")
         if self.hp_grad_weight:
             parts.append("hp_grad_weight=True")
+        if self.nf_aware_scaling:
+            parts.append("nf_aware_scaling=True")
         if self.delayed_scaling:
             parts.append("delayed_scaling=True")
         if self.use_fused_kernel:

@@ -24,8 +24,7 @@ class RMSNorm(nn.Module):
         self.eps = eps
 
     def forward(self, x):
-        xf = x.float()
-        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.eps) * self.weight).to(x.dtype)
+        return F.rms_norm(x, (x.shape[-1],), self.weight.to(x.dtype), self.eps)
 
 
 class DecoderLayer(nn.Module):

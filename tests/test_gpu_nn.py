@@ -280,3 +280,29 @@ def test_layer_step_replays_from_a_cuda_graph(kw):
     torch.cuda.synchronize()
     assert torch.equal(y_static, y_eager)
     assert torch.equal(dw_static, dw_eager) and torch.equal(dx_static, dx_eager)
+
+
+def test_nf_aware_scaling_matches_reference_formula():
+    """tcfp/core.py:161-193 and the layer branch at tcfp/nn/__init__.py:356-359:
+    scale from 3 sigma, outliers clipped; compared with the oracle given the
+    same (GPU-computed) standard deviation."""
+    from tcfp_b200.core import nf_aware_target_max, to_fp8_e4m3_nf_aware
+    from tcfp_b200.nn import TCFPLinear
+
+    w = weights(80, 128, 256, outliers=True)
+    tgt = nf_aware_target_max(w.to(DEV))
+    assert abs(tgt.item() - O.nf_aware_target_max(w).item()) / tgt.item() < 1e-5
+    q, inv = to_fp8_e4m3_nf_aware(w.to(DEV))
+    q_ref, inv_ref = O.to_fp8_e4m3(w, scale=(448.0 / tgt.cpu()).to(torch.float32))
+    assert torch.equal(q.cpu().view(torch.uint8), q_ref.view(torch.uint8)) and torch.equal(inv.cpu(), inv_ref)
+    assert int((q.float().abs() == 448).sum()) > 0                      # clipped outliers
+    layer = TCFPLinear(256, 128, bias=False, use_tensor_cores=True, nf_aware_scaling=True).to(DEV)
+    layer._param_name = "nf"
+    with torch.no_grad():
+        layer.weight.copy_(w)
+    x = acts(81, 64, 256, torch.float32)
+    y = layer(x.to(DEV))
+    hi, lo, ihi, ilo, err, _, _ = O.dual_quantize_per_tensor(w, torch.zeros_like(w), amax_hi=tgt.cpu())
+    a, ia = O.to_fp8_e4m3(x)
+    assert rel_fro(y, O.dual_gemm_nt(a, ia, hi, ihi, lo, ilo)) <= 1e-3
+    assert torch.equal(layer._error_state._buffers["nf"].cpu().view(torch.int32), err.view(torch.int32))
