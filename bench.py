@@ -31,7 +31,7 @@ sys.path.insert(0, str(ROOT))
 M = N = K = 8192
 BS = 64
 FLOP_PER_STEP = 4.0 * M * N * K
-WORKLOAD = "block-scaled TCFP-12 dual GEMM forward, M=N=K=8192, block 64 (BASELINE.json configs[2])"
+WORKLOAD = "block-scaled TCFP-12 dual GEMM forward, M=N=K=8192, block 64 (benchmark configuration 2)"
 
 
 def _peaks() -> dict:
@@ -123,7 +123,7 @@ def _cpu_sample(rows: int, passes: int):
 
 
 def _mlp_train_step_ms(world: int, dev, timed_fn) -> dict:
-    """BASELINE.json configs[0] on the GPU path: MLP 1024->4096->1024 (GELU),
+    """Benchmark configuration 0 on the GPU path: MLP 1024->4096->1024 (GELU),
     8192 tokens bf16, per-tensor scaling with error feedback, Adam; one step =
     zero_grad / forward / MSE / backward / optimizer step.  With N > 1 the MLP
     is tensor-parallel (column-parallel up, row-parallel down, one NCCL
@@ -182,8 +182,8 @@ def _mlp_train_step_ms(world: int, dev, timed_fn) -> dict:
 
 
 def run_train_workload(args) -> None:
-    """``--workload mlp_large`` (BASELINE.json configs[3]: MLP 4096->16384->4096, 32768 tokens, SRR, AdamW) and
-    ``--workload decoder`` (configs[4]: 4 Llama-style layers, d=4096, 32 heads, FFN 11008, 8x4096 tokens, block-64
+    """``--workload mlp_large`` (benchmark configuration 3: MLP 4096->16384->4096, 32768 tokens, SRR, AdamW) and
+    ``--workload decoder`` (configuration 4: 4 Llama-style layers, d=4096, 32 heads, FFN 11008, 8x4096 tokens, block-64
     EF), tensor-parallel over the launched ranks.  Prints one JSON line with the step time."""
     import torch
     import torch.distributed as dist
@@ -364,7 +364,7 @@ def run_ours(args) -> None:
         "pct_of_nominal_fp8_peak": per_gpu / 4500.0,
         "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": fp8_peak, "unit": "TFLOP/s",
                      "frac": per_gpu / fp8_peak, "traffic": 880.0e6,
-                     "traffic_note": "dram__bytes_read+write per launch from ncu on this workload (profiles/dual_gemm_pair_mxf8_8192_bench.md); algorithmic 448 MB",
+                     "traffic_note": "dram__bytes_read + dram__bytes_write per launch, ncu on this same command; algorithmic 448 MB",
                      "peak_source": f"2 x {peaks['src']} cuBLAS bf16 burst ({peaks['bf16']} TFLOP/s): no FP8 peak was measured; "
                                     "FP8 tensor rate is twice the bf16 rate",
                      "kernel": "dual_gemm_pair_kernel<KIND_MXF8>", "flop_per_launch": FLOP_PER_STEP},

@@ -26,7 +26,9 @@ import torch
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent.parent
 sys.path.insert(0, str(ROOT))
-ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: make_golden.py <path to a checkout of the reference project>")
+ref_root = sys.argv[1]
 sys.path.append(ref_root)  # after the repo root: both trees have a ``tests`` package
 
 import tcfp.core as rcore  # noqa: E402
