@@ -306,3 +306,57 @@ def test_nf_aware_scaling_matches_reference_formula():
     a, ia = O.to_fp8_e4m3(x)
     assert rel_fro(y, O.dual_gemm_nt(a, ia, hi, ihi, lo, ilo)) <= 1e-3
     assert torch.equal(layer._error_state._buffers["nf"].cpu().view(torch.int32), err.view(torch.int32))
+
+
+def test_abd_forward_identical_and_two_gemm_beats_one():
+    """tests/test_tensor_cores.py:390-406 (ABD changes only the backward) and
+    tests/test_tcfp12_tensor_cores.py:41-79 (the W_hi + W_lo decomposition is
+    closer to the FP32 layer than W_hi alone) of the reference."""
+    from tcfp_b200.kernels import fused_dual_gemm_forward
+    from tcfp_b200.core import dual_quantize_per_tensor, to_fp8_e4m3
+    from tcfp_b200.nn import TCFPLinear
+
+    torch.manual_seed(11)
+    x = torch.randn(256, 512, device=DEV)
+    for kw in (dict(), dict(scale_block_size=32)):
+        a = TCFPLinear(512, 256, use_tensor_cores=True, **kw).to(DEV)
+        b = TCFPLinear(512, 256, use_tensor_cores=True, abd=True, **kw).to(DEV)
+        b.load_state_dict(a.state_dict())
+        ya, yb = a(x), b(x)
+        assert torch.equal(ya, yb)
+        ref = torch.nn.functional.linear(x, a.weight, a.bias)
+        assert float((ya - ref).norm() / ref.norm()) < 0.1
+        xa = x.clone().requires_grad_(True)
+        xb = x.clone().requires_grad_(True)
+        a(xa).sum().backward()
+        b(xb).sum().backward()
+        # dropping W_lo from dX changes it only slightly
+        assert 0 < float((xa.grad - xb.grad).norm() / xa.grad.norm()) < 0.1
+    w = torch.randn(256, 512, device=DEV)
+    hi, lo, ihi, ilo, _ = dual_quantize_per_tensor(w)
+    aq, ia = to_fp8_e4m3(x)
+    exact = (aq.float() * ia) @ w.t()
+    two = fused_dual_gemm_forward(aq, hi, lo, ia, ihi, ilo)
+    one = fused_dual_gemm_forward(aq, hi, None, ia, ihi, None)
+    assert float((two - exact).norm()) < 0.25 * float((one - exact).norm())
+
+
+def test_error_feedback_reduces_accumulated_error():
+    """tests/test_tcfp12_tensor_cores.py:194-218: with the error buffer the
+    running mean of the dequantized weight tracks the FP32 weight better than
+    without it."""
+    from tcfp_b200.core import dual_quantize_per_tensor
+
+    w = weights(90, 256, 512, std=1.0).to(DEV)
+    err = torch.zeros_like(w)
+    acc_ef = torch.zeros_like(w)
+    acc_no = torch.zeros_like(w)
+    n = 16
+    for _ in range(n):
+        hi, lo, ihi, ilo, _ = dual_quantize_per_tensor(w, err)
+        acc_ef += hi.float() * ihi + lo.float() * ilo
+        hi, lo, ihi, ilo, _ = dual_quantize_per_tensor(w)
+        acc_no += hi.float() * ihi + lo.float() * ilo
+    e_ef = float((acc_ef / n - w).norm())
+    e_no = float((acc_no / n - w).norm())
+    assert err.abs().max() > 0 and e_ef < 0.5 * e_no
