@@ -214,14 +214,35 @@ def run_train_workload(args) -> None:
         lin = 4 * (4 * d * d + 3 * d * 11008)
         flop = 2 * x.shape[0] * x.shape[1] * lin * 5.0              # (2 fwd + 2 dX + 1 dW) products
     target = torch.randn(x.shape, generator=g).to(torch.bfloat16).to(dev)
-    opt = torch.optim.AdamW(model.parameters(), lr=3e-4)
+    use_graph = args.graph and args.workload == "decoder"   # SRR advances a host-side stream offset: not capturable
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-4, capturable=use_graph)
 
-    def step():
-        opt.zero_grad(set_to_none=True)
+    def eager_step():
+        opt.zero_grad(set_to_none=not use_graph)
         loss = torch.nn.functional.mse_loss(model(x).float(), target.float())
         loss.backward()
         opt.step()
         return loss
+
+    step = eager_step
+    if use_graph:
+        # the whole step -- quantizers, GEMMs, NCCL all-reduces, AdamW -- captured once and replayed
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                eager_step()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            static_loss = eager_step()
+
+        def step():
+            graph.replay()
+            return static_loss
 
     def barrier():
         torch.cuda.synchronize()
@@ -250,7 +271,7 @@ def run_train_workload(args) -> None:
             "metric": "train_step_ms", "value": ms_per_step, "unit": "ms", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "strong",
             "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
-            "config": {"workload": desc, "parallelism": f"tp{world}"},
+            "config": {"workload": desc, "parallelism": f"tp{world}", "cuda_graph": bool(use_graph)},
             "linear_tflops_effective": flop / (ms_per_step * 1e-3) / 1e12, "loss": float(loss.item()),
             "clocks": clk.summary(), "peak_mem_gb": torch.cuda.max_memory_allocated() / 2**30,
         }), flush=True)
@@ -397,6 +418,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gemm", choices=["gemm", "mlp_large", "decoder"])
+    ap.add_argument("--graph", action="store_true", help="decoder workload: replay the step from a CUDA graph")
     args = ap.parse_args()
     if args.workload != "gemm" and args.impl == "ours":
         run_train_workload(args)

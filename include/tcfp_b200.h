@@ -67,6 +67,10 @@ int32_t tcfp_last_error(char* buf, size_t n);
  * library recorded a timed-out wait since the last call (and clears the
  * record).  The hot path never calls this; tests and debug builds do. */
 int32_t tcfp_check_device_status(void* stream);
+/* Launches one CTA that waits limit_ns (at most 100 ms) on a barrier nothing
+ * signals, so that the give-up path -- status word set, kernel returns, the
+ * context stays usable -- can be tested without any real failure. */
+int32_t tcfp_selftest_bounded_wait(uint64_t limit_ns, void* stream);
 
 /* ---- K1: weight dual quantizer ----------------------------------------- */
 /*

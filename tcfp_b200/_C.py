@@ -23,6 +23,7 @@ _SIGNATURES = {
     "tcfp_version": (c_int32, []),
     "tcfp_last_error": (c_int32, [c_char_p, c_size_t]),
     "tcfp_check_device_status": (c_int32, [c_void_p]),
+    "tcfp_selftest_bounded_wait": (c_int32, [c_uint64, c_void_p]),
     "tcfp_dual_quantize": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                      c_void_p, c_void_p, c_int64, c_int64, c_int32, c_int32, c_uint64, c_uint64,
                                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),

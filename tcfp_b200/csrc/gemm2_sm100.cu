@@ -540,10 +540,13 @@ int launch2(const void* a, const void* b_hi, const void* b_lo, const void* sf_a,
   p.has_lo = b_lo != nullptr;
   constexpr int smem = smem_bytes2<KIND>();
   auto kern = dual_gemm_pair_kernel<KIND, B_MN, OUT_BF16, A_MN>;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[64] = {false};  // per template instance and device
+  int dev = 0;
+  CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(TCFP_ERR_UNSUPPORTED, "device index %d out of range", dev);
+  if (!configured[dev]) {
     CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    configured = true;
+    configured[dev] = true;
   }
   const int tile_n = (!T::kSum && !p.has_lo) ? 2 * BN : BN;
   const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + tile_n - 1) / tile_n);

@@ -460,10 +460,13 @@ int launch(const void* a, const void* b_hi, const void* b_lo, void* out, GemmPar
   p.has_lo = b_lo != nullptr;
   constexpr int smem = smem_bytes<KIND, OUT_BF16>();
   auto kern = dual_gemm_kernel<KIND, B_MN, OUT_BF16, A_MN>;
-  static bool configured = false;  // per template instance
-  if (!configured) {
+  static bool configured[64] = {false};  // per template instance and device
+  int dev = 0;
+  CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(TCFP_ERR_UNSUPPORTED, "device index %d out of range", dev);
+  if (!configured[dev]) {
     CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    configured = true;
+    configured[dev] = true;
   }
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
   const int grid = tiles < sm_count() ? tiles : sm_count();
@@ -481,6 +484,19 @@ bool use_pair_kernel(int64_t M) {
     forced = (e && e[0] == '1') ? 1 : 0;
   }
   return forced == 0 && M >= 256;
+}
+
+// One CTA waits, with the given limit, on a barrier nothing ever arrives on: exercises the
+// give-up path of mbar_wait (status word, orderly return) without any real failure.
+__global__ void bounded_wait_selftest_kernel(unsigned int* status, unsigned long long limit_ns) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_wait(smem_u32(&bar), 0, &abort_flag, status, limit_ns);
+  }
 }
 
 int check_dims(const char* who, int64_t M, int64_t N, int64_t K) {
@@ -503,6 +519,15 @@ extern "C" int32_t tcfp_check_device_status(void* stream) {
     CUDA_TRY(cudaMemcpyToSymbol(g_device_status, &zero, sizeof(zero)));
     return fail(TCFP_ERR_DEVICE, "a kernel gave up a bounded wait (status word 0x%x)", st);
   }
+  return TCFP_OK;
+}
+
+extern "C" int32_t tcfp_selftest_bounded_wait(uint64_t limit_ns, void* stream) {
+  if (limit_ns == 0 || limit_ns > 100000000ull) return fail(TCFP_ERR_INVALID, "selftest: limit must be in (0, 100 ms]");
+  unsigned int* st = device_status_ptr();
+  if (!st) return fail(TCFP_ERR_CUDA, "selftest: status word lookup failed");
+  bounded_wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(st, (unsigned long long)limit_ns);
+  CUDA_TRY(cudaGetLastError());
   return TCFP_OK;
 }
 

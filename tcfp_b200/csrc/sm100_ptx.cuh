@@ -51,7 +51,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false when the CTA is aborting.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          unsigned int* status) {
+                                          unsigned int* status, unsigned long long limit_ns = kWaitLimitNs) {
 #pragma unroll 1
   for (int i = 0; i < 128; ++i)
     if (mbar_try_wait(bar, parity)) return true;
@@ -60,7 +60,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (globaltimer_ns() - t0 > kWaitLimitNs) {
+    if (globaltimer_ns() - t0 > limit_ns) {
       *abort_flag = 1;
       if (status) atomicOr(status, 1u);
       return false;

@@ -185,3 +185,22 @@ def test_bf16_output_and_bias_on_pair_kernel():
     assert rel_fro(out.float(), O.dual_gemm_nn(gq, ig, whi, ihi, wlo, ilo)) <= 5e-3
     single = fused_dual_gemm_backward_dx(d(gq), d(whi), None, d(ig), d(ihi), None)
     assert rel_fro(single, O.dual_gemm_nn(gq, ig, whi, ihi, None, None)) <= TOL
+
+
+def test_bounded_wait_gives_up_and_reports(lib):
+    """A wait that nothing satisfies ends after its limit, the status word
+    records it, the host reads it as TCFP_ERR_DEVICE, and the context keeps
+    working."""
+    from tcfp_b200 import _C
+    from tcfp_b200.kernels import fused_dual_gemm_forward
+
+    _C.check_device_status()                                    # clean before
+    _C.check(lib.tcfp_selftest_bounded_wait(1_000_000, _C.stream()))     # 1 ms
+    with pytest.raises(RuntimeError, match="bounded wait"):
+        _C.check_device_status()
+    _C.check_device_status()                                    # the record was cleared
+    a, ia, hi, ihi, lo, ilo = _per_tensor_operands(102, 128, 128, 128)
+    d = lambda t: t.to(DEV)
+    out = fused_dual_gemm_forward(d(a), d(hi), d(lo), d(ia), d(ihi), d(ilo))
+    assert rel_fro(out, O.dual_gemm_nt(a, ia, hi, ihi, lo, ilo)) <= TOL
+    assert lib.tcfp_selftest_bounded_wait(0, None) == -1
