@@ -214,7 +214,9 @@ def run_train_workload(args) -> None:
         lin = 4 * (4 * d * d + 3 * d * 11008)
         flop = 2 * x.shape[0] * x.shape[1] * lin * 5.0              # (2 fwd + 2 dX + 1 dW) products
     target = torch.randn(x.shape, generator=g).to(torch.bfloat16).to(dev)
-    use_graph = args.graph and args.workload == "decoder"   # SRR advances a host-side stream offset: not capturable
+    # SRR advances a host-side stream offset (not capturable); with more than one rank the capture of the
+    # NCCL all-reduces did not complete in the one attempt made, so replay is offered on a single GPU only
+    use_graph = args.graph and args.workload == "decoder" and world == 1
     opt = torch.optim.AdamW(model.parameters(), lr=3e-4, capturable=use_graph)
 
     def eager_step():
