@@ -6,10 +6,13 @@ Every function cites the reference file:line it follows (paths are relative
 to the reference project root).  The per-tensor functions are pinned
 bit-for-bit against the reference itself, imported on CPU, by the golden
 fixtures in ``tests/golden`` (generator: ``tests/golden/make_golden.py``).
-The block-scaled functions restate Triton kernels that cannot execute without
-a GPU; they are pinned by the differential properties the reference's own
-tests assert (fused == two sequential block quantizes, the error-feedback
-formula, sentinel handling) -- parity for those is otherwise UNPINNED.
+The block-scaled functions restate Triton kernels; they are pinned against
+the reference's own kernel bodies executed on CPU by the Triton interpreter
+(``tests/golden/make_golden_block.py`` -> ``tests/golden/block_path.npz``):
+exponent planes, the zero-residual sentinel, the stochastic-rounding stream
+and the two GEMM formulas bit-for-bit / to 1e-5, FP8 codes everywhere except
+on the elements the interpreter's (not the hardware's) FP8 cast gets wrong --
+see ``tests/test_oracle_block_golden.py``.
 
 Conventions: weights ``(N, K)`` row-major, activations ``(M, K)``, block
 exponent planes ``(K // bs, rows)`` int8 with ``-128`` as the zero-residual

@@ -34,3 +34,31 @@ def layer_inputs(cfg):
     b = torch.randn(N, generator=g) * 0.1 if cfg["bias"] else None
     target = torch.randn(*x.shape[:-1], N, generator=g)
     return x, w, b, target
+
+
+# block-scaled path: weight (N, K), activation (M, K), gradient (M, N); N and K multiples of the block
+BLOCK_CASES = {
+    "bs32_ef": dict(seed=201, M=64, N=64, K=128, bs=32, ef=True),
+    "bs64_ef": dict(seed=202, M=64, N=128, K=128, bs=64, ef=True),
+    "bs128_noef": dict(seed=203, M=64, N=128, K=256, bs=128, ef=False),
+    "bs32_zero_rows": dict(seed=204, M=32, N=64, K=64, bs=32, ef=True, zero_rows=True),
+    "bs64_srr": dict(seed=205, M=32, N=64, K=128, bs=64, ef=False, srr_seed=1234567),
+}
+
+
+def block_inputs(cfg):
+    g = torch.Generator().manual_seed(cfg["seed"])
+    N, K, M = cfg["N"], cfg["K"], cfg["M"]
+    w = torch.randn(N, K, generator=g) * 0.02
+    mask = torch.rand(N, K, generator=g) < 0.01
+    w = torch.where(mask, w * 50.0, w)
+    if cfg.get("zero_rows"):
+        w[0] = 0.0            # amax floor
+        w[1] = 1.0            # exactly representable: zero residual -> sentinel
+        w[2, :32] = 448.0 * 2.0**-9
+    err = torch.randn(N, K, generator=g) * 1e-4 if cfg["ef"] else None
+    if cfg.get("zero_rows") and err is not None:
+        err[:3] = 0.0
+    x = (torch.randn(M, K, generator=g) * 1.5).to(torch.bfloat16)
+    gr = torch.randn(M, N, generator=g) * 0.01
+    return w, err, x, gr
