@@ -28,16 +28,15 @@ from .core import (
     to_fp8_e5m2,
 )
 from .kernels import (
-    block_dequantize_fp8,
+    bf16_weight_grad,
+    block_dequantize_bf16,
     block_quantize_fp8,
+    fp8_weight_grad,
     fused_block_scaled_backward_dx,
     fused_block_scaled_dual_gemm_forward,
     fused_dual_gemm_backward_dx,
     fused_dual_gemm_forward,
     fused_dual_quantize_fp8,
-    bf16_weight_grad,
-    block_dequantize_bf16,
-    fp8_weight_grad,
 )
 
 
