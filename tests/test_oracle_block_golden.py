@@ -124,3 +124,17 @@ def test_block_gemms_match_reference_kernels(name):
     dx_o = O.block_backward_dx(g, eg, hi, eh, lo, el, bs)
     assert float((y - y_o).norm() / y_o.norm()) <= 1e-5
     assert float((dx - dx_o).norm() / dx_o.norm()) <= 1e-5
+
+
+@pytest.mark.parametrize("name", list(BLOCK_CASES))
+def test_full_oracle_pipeline_through_the_shared_checker(name):
+    """The same checker the GPU test uses, fed with the oracle's end-to-end
+    outputs (W_lo computed from the oracle's own W_hi)."""
+    from tests.block_golden_check import check_block_quantize, check_dual_quantize
+
+    cfg = BLOCK_CASES[name]
+    w, err, x, g = block_inputs(cfg)
+    hi, lo, eh, el, _ = O.dual_quantize_block(w, cfg["bs"], err, srr="srr_seed" in cfg, seed=cfg.get("srr_seed", 0))
+    check_dual_quantize(name, hi, lo, eh, el)
+    check_block_quantize(name, "act", *O.block_quantize(x, cfg["bs"], E4))
+    check_block_quantize(name, "grad", *O.block_quantize(g, cfg["bs"], E5))
