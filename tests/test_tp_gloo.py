@@ -66,6 +66,18 @@ def _worker(rank: int, world: int, port: int, ret):
         ok &= torch.allclose(mlp.up.inner.weight.grad, ref_up.weight.grad[s:e], atol=1e-5)
         ok &= torch.allclose(mlp.down.inner.weight.grad, ref_down.weight.grad[:, s:e], atol=1e-5)
         ok &= torch.allclose(mlp.down.bias.grad, ref_down.bias.grad, atol=1e-5)
+        # sequence-parallel form: token shards in, token shards out, same numbers
+        sp = ParallelMLP(d, h, granule=granule, layer_factory=factory, sequence_parallel=True)
+        sp.load_state_dict(mlp.state_dict())
+        rows = x.shape[0] // world
+        xs = x[rank * rows:(rank + 1) * rows].clone().requires_grad_(True)
+        ys = sp(xs)
+        ((ys - target[rank * rows:(rank + 1) * rows]) ** 2).sum().div(target.numel()).backward()
+        ok &= ys.shape == (rows, d) and torch.allclose(ys, y_ref[rank * rows:(rank + 1) * rows], atol=1e-5)
+        ok &= torch.allclose(xs.grad, xr.grad[rank * rows:(rank + 1) * rows], atol=1e-5)
+        ok &= torch.allclose(sp.up.inner.weight.grad, ref_up.weight.grad[s:e], atol=1e-5)
+        ok &= torch.allclose(sp.down.inner.weight.grad, ref_down.weight.grad[:, s:e], atol=1e-5)
+        ok &= torch.allclose(sp.down.bias.grad, ref_down.bias.grad, atol=1e-5)
         ret[rank] = bool(ok)
     finally:
         dist.destroy_process_group()
