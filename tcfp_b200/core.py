@@ -170,75 +170,87 @@ def fp8_matmul_nn(a_fp8: torch.Tensor, b_fp8_t: torch.Tensor, scale_a: torch.Ten
 
 
 class ErrorFeedbackState:
-    """Per-parameter state of the tensor-core path; same five dictionaries,
-    keys and update rules as tcfp/core.py:298-410, so ``ef_state.pt``
-    checkpoints written by either implementation load in the other
-    (tcfp/training/checkpointing.py:200-271)."""
+    """Per-parameter state of the tensor-core path.
+
+    Five dictionaries with the reference's names and key scheme
+    (tcfp/core.py:298-410) -- ``_buffers[name]`` the FP32 error buffer,
+    ``_amax_ema``, ``_delayed_amax[name + ".w_hi"]``, ``_residual_ratio[name +
+    ".ratio"]`` and ``_step_count[name + ".steps"]`` -- so that ``ef_state.pt``
+    files written by either implementation load in the other
+    (tcfp/training/checkpointing.py:200-271).  All moving averages are
+    ``decay * previous + (1 - decay) * new`` evaluated in that order on device
+    tensors; nothing here synchronises with the host except the step counter,
+    which is a host integer by design."""
 
     def __init__(self, ema_decay: float = 0.999, residual_validation_interval: int = 100) -> None:
         self._buffers: dict[str, torch.Tensor] = {}
         self._amax_ema: dict[str, torch.Tensor] = {}
-        self._ema_decay: float = ema_decay
         self._delayed_amax: dict[str, torch.Tensor] = {}
         self._residual_ratio: dict[str, torch.Tensor] = {}
         self._step_count: dict[str, int] = {}
+        self._ema_decay: float = ema_decay
         self._residual_validation_interval: int = residual_validation_interval
 
+    # -- shared moving-average step ---------------------------------------
+    def _blend(self, table: dict[str, torch.Tensor], key: str, value: torch.Tensor) -> tuple[torch.Tensor, bool]:
+        """Folds ``value`` into ``table[key]``; returns (stored value, was_first)."""
+        value = value.detach()
+        if key not in table:
+            return value, True
+        d = self._ema_decay
+        table[key] = d * table[key] + (1 - d) * value
+        return table[key], False
+
+    # -- error buffer -------------------------------------------------------
     def get_error(self, name: str, like: torch.Tensor) -> torch.Tensor:
-        # tcfp/core.py:320-323
-        if name not in self._buffers or self._buffers[name].shape != like.shape:
-            self._buffers[name] = torch.zeros_like(like, dtype=torch.float32)
-        return self._buffers[name]
+        """The buffer for ``name``: FP32, zero on first use or after a shape change."""
+        buf = self._buffers.get(name)
+        if buf is None or buf.shape != like.shape:
+            buf = torch.zeros_like(like, dtype=torch.float32)
+            self._buffers[name] = buf
+        return buf
 
     def update_error(self, name: str, error: torch.Tensor) -> None:
         self._buffers[name] = error.detach()
 
+    # -- amax tracking --------------------------------------------------------
     def get_amax_ema(self, name: str, current_amax: torch.Tensor) -> torch.Tensor:
-        if name not in self._amax_ema:
-            self._amax_ema[name] = current_amax.detach().clone()
-        else:
-            self._amax_ema[name] = (
-                self._ema_decay * self._amax_ema[name] + (1 - self._ema_decay) * current_amax.detach()
-            )
+        stored, first = self._blend(self._amax_ema, name, current_amax)
+        if first:
+            self._amax_ema[name] = stored.clone()
         return self._amax_ema[name]
 
     def get_delayed_amax(self, name: str, current_amax: torch.Tensor) -> torch.Tensor:
-        # tcfp/core.py:341-358: first call returns the current amax unchanged
-        if name not in self._delayed_amax:
-            self._delayed_amax[name] = current_amax.detach().clone()
+        """Delayed-scaling amax: the very first call stores and returns the
+        current value unchanged (no delay on step 0), later calls return the
+        moving average that already includes the current value."""
+        stored, first = self._blend(self._delayed_amax, name, current_amax)
+        if first:
+            self._delayed_amax[name] = stored.clone()
             return current_amax
-        prev = self._delayed_amax[name]
-        self._delayed_amax[name] = self._ema_decay * prev + (1 - self._ema_decay) * current_amax.detach()
-        return self._delayed_amax[name]
+        return stored
 
     def predict_residual_amax(self, name: str, main_amax: torch.Tensor) -> torch.Tensor:
-        # tcfp/core.py:360-372
-        ratio_key = f"{name}.ratio"
-        if ratio_key not in self._residual_ratio:
-            return (main_amax / 8.0).clamp(min=1e-12)
-        return (main_amax * self._residual_ratio[ratio_key]).clamp(min=1e-12)
+        """Residual amax predicted from the main one: tracked ratio, or 1/8
+        (three mantissa bits) before any ratio was observed."""
+        ratio = self._residual_ratio.get(f"{name}.ratio")
+        predicted = main_amax / 8.0 if ratio is None else main_amax * ratio
+        return predicted.clamp(min=1e-12)
 
     def update_residual_ratio(self, name: str, main_amax: torch.Tensor, actual_residual_amax: torch.Tensor) -> None:
-        # tcfp/core.py:374-391
-        ratio = (actual_residual_amax / main_amax.clamp(min=1e-12)).detach()
-        ratio_key = f"{name}.ratio"
-        if ratio_key not in self._residual_ratio:
-            self._residual_ratio[ratio_key] = ratio
-        else:
-            self._residual_ratio[ratio_key] = (
-                self._ema_decay * self._residual_ratio[ratio_key] + (1 - self._ema_decay) * ratio
-            )
+        key = f"{name}.ratio"
+        ratio = actual_residual_amax / main_amax.clamp(min=1e-12)
+        stored, first = self._blend(self._residual_ratio, key, ratio)
+        if first:
+            self._residual_ratio[key] = stored
 
     def should_validate_residual(self, name: str) -> bool:
-        # tcfp/core.py:393-403
+        """True on the first call and on every ``residual_validation_interval``-th."""
         key = f"{name}.steps"
-        count = self._step_count.get(key, 0) + 1
-        self._step_count[key] = count
-        return count == 1 or count % self._residual_validation_interval == 0
+        n = self._step_count.get(key, 0) + 1
+        self._step_count[key] = n
+        return n == 1 or n % self._residual_validation_interval == 0
 
     def reset(self) -> None:
-        self._buffers.clear()
-        self._amax_ema.clear()
-        self._delayed_amax.clear()
-        self._residual_ratio.clear()
-        self._step_count.clear()
+        for table in (self._buffers, self._amax_ema, self._delayed_amax, self._residual_ratio, self._step_count):
+            table.clear()

@@ -100,3 +100,40 @@ def test_srr_stream_position_is_checkpointed(tmp_path):
     n = torch.nn.Sequential(TCFPLinear(32, 32, use_tensor_cores=True, srr=True, srr_seed=9))
     load_ef_state(n, tmp_path / "s.pt")
     assert n[0].srr_seed == 5 and n[0]._srr_offset == 4096
+
+
+def test_state_machine_is_bit_identical_to_the_reference_class():
+    """Differential run against the reference's own ``ErrorFeedbackState``
+    when its checkout is available (it is where the goldens are generated;
+    it is not on the GPU box, where this test skips)."""
+    import importlib.util
+    import random
+    import sys
+
+    import pytest
+
+    ref_root = Path("/root/reference")
+    if not (ref_root / "tcfp" / "core.py").exists():
+        pytest.skip("reference checkout not present")
+    spec = importlib.util.spec_from_file_location("_ref_tcfp_core", ref_root / "tcfp" / "core.py")
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[spec.name] = mod
+    spec.loader.exec_module(mod)
+    r, o = mod.ErrorFeedbackState(residual_validation_interval=7), ErrorFeedbackState(residual_validation_interval=7)
+    torch.manual_seed(0)
+    random.seed(0)
+    for i in range(200):
+        a = torch.rand(()) * 3 + 0.01
+        b = torch.rand(()) * 0.5 + 0.001
+        for name in ("x", "y"):
+            assert torch.equal(r.get_delayed_amax(name + ".w_hi", a), o.get_delayed_amax(name + ".w_hi", a))
+            assert torch.equal(r.get_amax_ema(name, a), o.get_amax_ema(name, a))
+            assert torch.equal(r.predict_residual_amax(name, a), o.predict_residual_amax(name, a))
+            assert r.should_validate_residual(name) == o.should_validate_residual(name)
+            if i % 3 == 0:
+                r.update_residual_ratio(name, a, b)
+                o.update_residual_ratio(name, a, b)
+    for table in ("_amax_ema", "_delayed_amax", "_residual_ratio"):
+        d1, d2 = getattr(r, table), getattr(o, table)
+        assert d1.keys() == d2.keys() and all(torch.equal(d1[k], d2[k]) for k in d1)
+    assert r._step_count == o._step_count
