@@ -112,7 +112,10 @@ def test_state_machine_is_bit_identical_to_the_reference_class():
 
     import pytest
 
-    ref_root = Path("/root/reference")
+    import os
+
+    # a checkout named "reference" next to this repository, or wherever TCFP_REFERENCE_ROOT points
+    ref_root = Path(os.environ.get("TCFP_REFERENCE_ROOT", Path(__file__).resolve().parents[2] / "reference"))
     if not (ref_root / "tcfp" / "core.py").exists():
         pytest.skip("reference checkout not present")
     spec = importlib.util.spec_from_file_location("_ref_tcfp_core", ref_root / "tcfp" / "core.py")
