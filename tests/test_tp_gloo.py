@@ -95,3 +95,35 @@ def test_parallel_mlp_matches_unsharded_world2():
         p.join(timeout=120)
         assert p.exitcode == 0
     assert all(ret.get(r) for r in range(world)), dict(ret)
+
+
+def test_block_aligned_shards_reproduce_the_unsharded_quantized_bytes():
+    """Column-parallel shards (rows of W) and row-parallel shards (K blocks of W
+    and of the activation) quantize to exactly the bytes of the unsharded
+    layer: block scales are per (row, K block).  Checked with the oracle."""
+    from oracle import tcfp_oracle as O
+    from tests.util import acts, weights
+
+    bs, world = 64, 4
+    N, K, M = 256, 704, 48                     # K = 11 blocks: uneven row-parallel shards (3,3,3,2)
+    w = weights(700, N, K, outliers=True)
+    err = weights(701, N, K, std=1e-4)
+    x = acts(702, M, K, torch.bfloat16)
+    hi, lo, eh, el, new_err = O.dual_quantize_block(w, bs, err)
+    a, ea = O.block_quantize(x, bs)
+    full = O.block_dual_gemm_nt(a, ea, hi, eh, lo, el, bs)
+    partial_sum = torch.zeros(M, N)
+    for r in range(world):
+        s, e = shard_bounds(N, world, r, bs)                       # column parallel: rows of W
+        h2, l2, eh2, el2, ne2 = O.dual_quantize_block(w[s:e].contiguous(), bs, err[s:e].contiguous())
+        assert torch.equal(h2.view(torch.uint8), hi[s:e].view(torch.uint8)) and torch.equal(l2.view(torch.uint8), lo[s:e].view(torch.uint8))
+        assert torch.equal(eh2, eh[:, s:e]) and torch.equal(el2, el[:, s:e]) and torch.equal(ne2, new_err[s:e])
+        ks, ke = shard_bounds(K, world, r, bs)                     # row parallel: K blocks
+        h3, l3, eh3, el3, ne3 = O.dual_quantize_block(w[:, ks:ke].contiguous(), bs, err[:, ks:ke].contiguous())
+        assert torch.equal(h3.view(torch.uint8), hi[:, ks:ke].view(torch.uint8))
+        assert torch.equal(l3.view(torch.uint8), lo[:, ks:ke].view(torch.uint8))
+        assert torch.equal(eh3, eh[ks // bs:ke // bs]) and torch.equal(ne3, new_err[:, ks:ke])
+        a3, ea3 = O.block_quantize(x[:, ks:ke].contiguous(), bs)
+        assert torch.equal(a3.view(torch.uint8), a[:, ks:ke].view(torch.uint8)) and torch.equal(ea3, ea[ks // bs:ke // bs])
+        partial_sum += O.block_dual_gemm_nt(a3, ea3, h3, eh3, l3, el3, bs)
+    assert float((partial_sum - full).norm() / full.norm()) <= 1e-6    # only the summation order differs
