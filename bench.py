@@ -1,6 +1,7 @@
 """Benchmark of the TCFP-12 hot path: block-scaled dual-FP8 GEMM at 8192^3.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload gemm|mlp|mlp_large|decoder] [--sp] [--no-extras]
 
 One "step" is one forward pass of the hot path over one batch: the fused
 block-scaled dual GEMM  out = X_q . W_hi^T + X_q . W_lo^T  (both products
@@ -9,16 +10,26 @@ counted: 4*M*N*K FLOP) on operands already quantized and resident in HBM.
 activation buffer: H2D copy, weight dual-quantize (error feedback), activation
 block-quantize, dual GEMM, D2H copy of the FP32 output.
 
-Under torchrun (N > 1) every rank owns one column shard of a layer whose
-output width is N*8192 (column parallel: no data-path collective), so the
-scaling is weak and ``value`` is the sum over ranks divided by the slowest
-rank's time.
+Under torchrun (N > 1) ``value`` is N independent column shards of a layer
+whose output width is N*8192 (no data-path collective: it shows that the GEMM
+path itself does not degrade, nothing about tensor-parallel scaling).  The
+tensor-parallel TRAINING steps, with their NCCL collectives inside the timed
+region, are reported in every line under ``extra``: ``mlp_train_step``
+(configuration 0), ``mlp_large_train_step`` (configuration 3) and
+``decoder_train_step`` (configuration 4), each with the step time, the time
+the same step takes with the collectives switched off, and the difference.
+
+``--impl reference`` times the CPU form of the reference's block-scaled path
+(its kernels are Triton and need a GPU) on all host cores, whole 8192-row
+passes; when a GPU and ``oracle/_ref`` are present it also reports, under
+``reference_gpu``, the reference's own GPU kernels on the same operands.
 """
 from __future__ import annotations
 
 import argparse
 import json
 import os
+import re
 import subprocess
 import sys
 import threading
@@ -32,22 +43,43 @@ M = N = K = 8192
 BS = 64
 FLOP_PER_STEP = 4.0 * M * N * K
 WORKLOAD = "block-scaled TCFP-12 dual GEMM forward, M=N=K=8192, block 64 (benchmark configuration 2)"
+PROFILE = ROOT / "profiles" / "dual_gemm_pair_mxf8_8192_bench.md"
+
+
+def _config(world: int) -> dict:
+    return {"workload": WORKLOAD,
+            "l2": "operands + output = 448 MB per step, larger than the 126 MB L2",
+            "parallelism": f"column-parallel shards x{world}, no collective" if world > 1 else "single GPU"}
 
 
 def _peaks() -> dict:
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
         d = json.loads(p.read_text())
-        return {"bf16": float(d["bf16_tflops"]), "hbm": float(d["hbm_gbs"]), "src": "measured"}
-    return {"bf16": 1590.0, "hbm": 6650.0, "src": "fallback"}
+        return {"bf16": float(d["bf16_tflops"]), "bf16_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                "hbm": float(d["hbm_gbs"]), "src": "measured"}
+    return {"bf16": 1590.0, "bf16_sustained": 1400.0, "hbm": 6650.0, "src": "fallback"}
+
+
+def _profiled_traffic():
+    """DRAM bytes per launch of the benchmark's kernel, from the kept ncu
+    summary (rows ``| launch | duration | clock | tensor % | read MB | write MB |``)."""
+    try:
+        rows = re.findall(r"^\|\s*\d+\s*\|.*?\|\s*([\d.]+)\s*MB\s*\|\s*([\d.]+)\s*MB\s*\|\s*$", PROFILE.read_text(), re.M)
+        if rows:
+            return sum(float(r) + float(w) for r, w in rows) / len(rows) * 1e6, str(PROFILE.relative_to(ROOT))
+    except OSError:
+        pass
+    return None, None
 
 
 class ClockSampler:
     """Samples SM clock and throttle reasons through NVML (read-only) in a
     background thread while the timed region runs."""
 
-    def __init__(self, index: int):
+    def __init__(self, index: int, period_s: float = 0.002):
         self.index = index
+        self.period = period_s
         self.sm: list[int] = []
         self.reasons_seen = 0
         self.sm_max = None
@@ -79,7 +111,7 @@ class ClockSampler:
                     self.sm_max = b
             except Exception:
                 pass
-            self._stop.wait(0.002)
+            self._stop.wait(self.period)
 
     def __enter__(self):
         self._thread.start()
@@ -93,13 +125,15 @@ class ClockSampler:
         sm = sorted(self.sm)
         names = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
         reasons = [n for bit, n in names.items() if self.reasons_seen & bit]
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": self.sm_max, "reasons": reasons,
-                "samples": len(sm)}
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_mhz_min": sm[0] if sm else None,
+                "sm_max_mhz": self.sm_max, "reasons": reasons, "samples": len(sm)}
 
 
-def _cpu_sample(rows: int, passes: int):
-    """The oracle's CPU form of the same step on the first ``rows`` activation
-    rows of the workload: dequantize, FP32 dual matmul.  Returns TFLOP/s."""
+# ---------------------------------------------------------------------------
+# CPU arm: the oracle's restatement of the reference's block path
+# ---------------------------------------------------------------------------
+
+def _cpu_operands():
     import torch
 
     from oracle import tcfp_oracle as O
@@ -107,89 +141,253 @@ def _cpu_sample(rows: int, passes: int):
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     g = torch.Generator().manual_seed(1003)
-    x = torch.randn(rows, K, generator=g).to(torch.bfloat16)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
     w = torch.randn(N, K, generator=g) * 0.02
     a, ea = O.block_quantize(x, BS)
     hi, lo, eh, el, _ = O.dual_quantize_block(w, BS)
-    O.block_dual_gemm_nt(a[:256], ea[:, :256].contiguous(), hi, eh, lo, el, BS)  # warm-up
+    return O, cores, (a, ea, hi, eh, lo, el)
+
+
+def _cpu_passes(passes: int, warmup: int):
+    """Whole passes of the workload on the host: dequantize + FP32 dual matmul
+    over all 8192 activation rows.  Returns (TFLOP/s from the mean pass,
+    cores, list of pass seconds)."""
+    O, cores, (a, ea, hi, eh, lo, el) = _cpu_operands()
+    for _ in range(warmup):
+        O.block_dual_gemm_nt(a, ea, hi, eh, lo, el, BS)
     times = []
     for _ in range(passes):
         t0 = time.perf_counter()
         O.block_dual_gemm_nt(a, ea, hi, eh, lo, el, BS)
         times.append(time.perf_counter() - t0)
-    times.sort()
-    med = times[len(times) // 2]
-    return 4.0 * rows * N * K / med / 1e12, cores, med
+    mean = sum(times) / len(times)
+    return FLOP_PER_STEP / mean / 1e12, cores, times
 
 
-def _mlp_train_step_ms(world: int, dev, timed_fn) -> dict:
-    """Benchmark configuration 0 on the GPU path: MLP 1024->4096->1024 (GELU),
-    8192 tokens bf16, per-tensor scaling with error feedback, Adam; one step =
-    zero_grad / forward / MSE / backward / optimizer step.  With N > 1 the MLP
-    is tensor-parallel (column-parallel up, row-parallel down, one NCCL
-    all-reduce forward and one backward)."""
+# ---------------------------------------------------------------------------
+# the reference's own GPU kernels, same box, same operands
+# ---------------------------------------------------------------------------
+
+def _reference_gpu(dev, a, s_a, w_hi, w_lo, s_hi, s_lo, x, w, ours_ms: float | None) -> dict:
+    """Times the reference's GPU paths for this step on the operands the
+    benchmark uses: its Triton block-scaled dual GEMM (tcfp/kernels.py:
+    1939-2028), its per-tensor fallback of two ``torch._scaled_mm`` plus an
+    add (tcfp/nn/__init__.py:405-421), its cuBLASLt extension
+    (tcfp/csrc/fused_dual_gemm.cu) and its Triton per-tensor kernel."""
     import torch
 
-    from tcfp_b200.nn import TCFPLinear
-    from tcfp_b200.tp import ParallelMLP
+    from oracle import ref_loader
 
-    d, h, tokens = 1024, 4096, 8192
-    g = torch.Generator().manual_seed(1001)
-    x = torch.randn(tokens, d, generator=g).to(torch.bfloat16).to(dev)
-    target = torch.randn(tokens, d, generator=g).to(dev)
-    torch.manual_seed(1001)
-    if world > 1:
-        model = ParallelMLP(d, h).to(dev)
+    if not ref_loader.available():
+        return {"unavailable": "oracle/_ref not built (python -m oracle.build_ref needs the reference checkout)"}
+    out: dict = {"operands": "the benchmark's own quantized operands, 8192^3; CUDA events, 5 launches after warm-up"}
+
+    def t(fn, n=5, warm=2):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    try:
+        ref_loader.load_reference()
+        import tcfp.cuda_ext as rc
+        import tcfp.kernels as rk
+
+        def entry(ms):
+            return {"ms": ms, "tflops": FLOP_PER_STEP / ms / 1e9}
+
+        if rk.is_triton_available():
+            y = rk.fused_block_scaled_dual_gemm_forward(a, w_hi, w_lo, s_a, s_hi, s_lo, BS)   # autotunes on first call
+            del y
+            out["triton_block_scaled_dual_gemm_bs64"] = entry(t(lambda: rk.fused_block_scaled_dual_gemm_forward(
+                a, w_hi, w_lo, s_a, s_hi, s_lo, BS)))
+        # per-tensor comparators on per-tensor operands of the same tensors
+        from tcfp_b200.core import dual_quantize_per_tensor, to_fp8_e4m3
+        from tcfp_b200.kernels import fused_dual_gemm_forward
+
+        p_hi, p_lo, i_hi, i_lo, _ = dual_quantize_per_tensor(w)
+        p_a, i_a = to_fp8_e4m3(x)
+
+        def two_scaled_mm():
+            y = torch._scaled_mm(p_a, p_hi.t(), scale_a=i_a, scale_b=i_hi, out_dtype=torch.float32)
+            y += torch._scaled_mm(p_a, p_lo.t(), scale_a=i_a, scale_b=i_lo, out_dtype=torch.float32)
+            return y
+
+        out["two_scaled_mm_plus_add_per_tensor"] = entry(t(two_scaled_mm))
+        if rk.is_triton_available():
+            rk.fused_dual_gemm_forward(p_a, p_hi, p_lo, i_a, i_hi, i_lo)
+            out["triton_per_tensor_dual_gemm"] = entry(t(lambda: rk.fused_dual_gemm_forward(p_a, p_hi, p_lo, i_a, i_hi, i_lo)))
+        if rc.is_cuda_ext_available():
+            out["cublaslt_ext_per_tensor"] = entry(t(lambda: rc.cuda_ext_dual_gemm_forward(p_a, p_hi, p_lo, i_a, i_hi, i_lo)))
+        out["ours_per_tensor_dual_gemm"] = entry(t(lambda: fused_dual_gemm_forward(p_a, p_hi, p_lo, i_a, i_hi, i_lo)))
+        if ours_ms is not None:
+            out["ours_block_scaled_dual_gemm_bs64"] = entry(ours_ms)
+            ref = out.get("triton_block_scaled_dual_gemm_bs64")
+            if ref:
+                out["speedup_vs_reference_block_kernel"] = ref["ms"] / ours_ms
+    except Exception as e:
+        out["error"] = repr(e)[:300]
+    finally:
+        ref_loader.unload()
+    return out
+
+
+# ---------------------------------------------------------------------------
+# training-step workloads (tensor parallel over the launched ranks)
+# ---------------------------------------------------------------------------
+
+TRAIN_DESC = {
+    "mlp": "MLP 1024->4096->1024 GELU, 64x128 tokens bf16, per-tensor EF, Adam, fwd+bwd+step (configuration 0)",
+    "mlp_large": "MLP 4096->16384->4096 GELU, 16x2048 tokens bf16, per-tensor SRR, AdamW, fwd+bwd+step (configuration 3)",
+    "decoder": "4 decoder layers d=4096 h=32 ffn=11008, batch 8 x seq 4096 bf16, block-64 EF, AdamW, fwd+bwd+step "
+               "(configuration 4)",
+}
+
+
+def _build_train_workload(name: str, dev, world: int, sp: bool):
+    import torch
+
+    from tcfp_b200.workloads import build_decoder, build_mlp
+
+    if name == "mlp":
+        d, h, tokens, seed = 1024, 4096, 64 * 128, 1001
+        model = build_mlp(d, h).to(dev)
+        opt_cls, lr = torch.optim.Adam, 1e-4
+        shape = (tokens, d)
+        flop = 2.0 * tokens * d * h * 2 * 5           # two layers x (2 fwd + 2 dX + 1 dW) products
+    elif name == "mlp_large":
+        d, h, tokens, seed = 4096, 16384, 16 * 2048, 1004
+        model = build_mlp(d, h, srr=True).to(dev)
+        opt_cls, lr = torch.optim.AdamW, 3e-4
+        shape = (tokens, d)
+        flop = 2.0 * tokens * d * h * 2 * 5
     else:
-        model = torch.nn.Sequential(TCFPLinear(d, h, use_tensor_cores=True), torch.nn.GELU(),
-                                    TCFPLinear(h, d, use_tensor_cores=True)).to(dev)
-        model[0]._param_name, model[2]._param_name = "fc1", "fc2"
-    opt = torch.optim.Adam(model.parameters(), lr=1e-4)
+        d, seed = 4096, 1005
+        model = build_decoder(sequence_parallel=sp).to(dev)
+        opt_cls, lr = torch.optim.AdamW, 3e-4
+        shape = (8, 4096, d)
+        flop = 2.0 * 8 * 4096 * 4 * (4 * d * d + 3 * d * 11008) * 5
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(shape, generator=g).to(torch.bfloat16).to(dev)
+    target = torch.randn(shape, generator=g).to(torch.bfloat16).to(dev)
+    opt = opt_cls(model.parameters(), lr=lr)
 
     def step():
         opt.zero_grad(set_to_none=True)
-        loss = torch.nn.functional.mse_loss(model(x), target)
+        loss = torch.nn.functional.mse_loss(model(x).float(), target.float())
         loss.backward()
         opt.step()
+        return loss
 
-    steps = 10
-    ms = timed_fn(step, steps, 3) / steps
-    res = {"config": "MLP 1024->4096->1024 GELU, 8192 tokens bf16, per-tensor EF, Adam, fwd+bwd+step",
-           "ms_per_step": ms, "parallelism": f"tp{world}" if world > 1 else "single GPU"}
-    if world == 1:
-        # the same step captured once in a CUDA graph and replayed: ~45 launches lose their launch gaps
-        try:
-            opt_g = torch.optim.Adam(model.parameters(), lr=1e-4, capturable=True)
+    return step, flop
 
-            def gstep():
-                opt_g.zero_grad(set_to_none=False)
-                torch.nn.functional.mse_loss(model(x), target).backward()
-                opt_g.step()
 
-            side = torch.cuda.Stream()
-            side.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(side):
-                for _ in range(3):
-                    gstep()
-            torch.cuda.current_stream().wait_stream(side)
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                gstep()
-            res["ms_per_step_cuda_graph"] = timed_fn(graph.replay, steps, 3) / steps
-        except Exception as e:
-            res["cuda_graph_error"] = repr(e)[:160]
+def _train_step_extra(name: str, dev, world: int, timed, steps: int, sp: bool = False) -> dict:
+    """One tensor-parallel training workload: ms per step with the NCCL
+    collectives inside the timed region, the same step with the collectives
+    switched off, and their difference (communication not hidden by compute)."""
+    import torch
+
+    from tcfp_b200 import tp
+
+    step, flop = _build_train_workload(name, dev, world, sp)
+    ms = timed(step, steps, 3) / steps
+    res = {"config": TRAIN_DESC[name], "parallelism": (f"tp{world}" + (" sequence-parallel" if sp else "")) if world > 1
+           else "single GPU", "ms_per_step": ms, "steps": steps,
+           "linear_tflops_effective": flop / (ms * 1e-3) / 1e12, "loss": float(step().item())}
+    if world > 1:
+        with tp.collectives_disabled():
+            ms_nocomm = timed(step, steps, 2) / steps
+        res["ms_per_step_collectives_off"] = ms_nocomm
+        res["comm_ms_per_step"] = max(0.0, ms - ms_nocomm)
+        res["collective"] = "NCCL all-reduce (bf16/fp32 partial outputs forward, input gradients backward)" if not sp \
+            else "NCCL all-gather + reduce-scatter"
+    res["peak_mem_gb"] = torch.cuda.max_memory_allocated() / 2**30
+    del step
+    torch.cuda.empty_cache()
     return res
 
 
+def _kernel_extras(dev, timed) -> dict:
+    """Driver-run figures for the other kernels of the path at 8192 x 8192
+    (inputs 128-512 MB, larger than L2): quantizers in GB/s of ALGORITHMIC
+    bytes, block 32 / 128 forward, dX (with and without the per-weight-version
+    re-targeting pass), dW."""
+    import torch
+
+    from tcfp_b200.core import dual_quantize_per_tensor, to_fp8_e4m3, to_fp8_e5m2
+    from tcfp_b200.kernels import (bf16_weight_grad, block_dequantize_bf16, block_quantize_fp8, block_retarget,
+                                   fp8_weight_grad, fused_block_scaled_backward_dx,
+                                   fused_block_scaled_dual_gemm_forward, fused_dual_quantize_fp8)
+
+    n = 8192
+    e = n * n
+    g = torch.Generator().manual_seed(7)
+    w = (torch.randn(n, n, generator=g) * 0.02).to(dev)
+    err = torch.zeros(n, n, device=dev)
+    x = torch.randn(n, n, generator=g).to(torch.bfloat16).to(dev)
+    gy = torch.randn(n, n, generator=g).to(dev)
+    hbm = _peaks()["hbm"]
+    out: dict = {"shape": "8192 x 8192", "hbm_peak_gbs": hbm}
+    iters = 10
+
+    def q(name, fn, bytes_per_elem):
+        ms = timed(fn, iters, 3) / iters
+        gbs = bytes_per_elem * e / ms / 1e6
+        out[name] = {"us": ms * 1e3, "algorithmic_bytes_per_elem": bytes_per_elem, "gbs": gbs, "frac_of_hbm": gbs / hbm}
+
+    for bs in (32, 64, 128):
+        q(f"dual_quantize_block{bs}_ef", lambda: fused_dual_quantize_fp8(w, bs, err), 14)
+    q("dual_quantize_block64_no_ef", lambda: fused_dual_quantize_fp8(w, 64, None), 6)
+    q("dual_quantize_block64_srr", lambda: fused_dual_quantize_fp8(w, 64, None, True, seed=1), 6)
+    q("act_quantize_block64_bf16_e4m3", lambda: block_quantize_fp8(x, 64), 3)
+    q("grad_quantize_block64_f32_e5m2", lambda: block_quantize_fp8(gy, 64, torch.float8_e5m2), 5)
+    q("dual_quantize_per_tensor_ef_fresh", lambda: dual_quantize_per_tensor(w, err), 14)
+    a_hi, a_lo = torch.tensor(0.1, device=dev), torch.tensor(0.0125, device=dev)
+    q("dual_quantize_per_tensor_ef_delayed", lambda: dual_quantize_per_tensor(w, err, amax_hi=a_hi, amax_lo=a_lo), 14)
+    q("dual_quantize_per_tensor_srr", lambda: dual_quantize_per_tensor(w, None, srr=True), 6)
+    q("act_cast_per_tensor_bf16_e4m3", lambda: to_fp8_e4m3(x), 3)
+    q("grad_cast_per_tensor_f32_e5m2", lambda: to_fp8_e5m2(gy), 5)
+
+    flop = 4.0 * n**3
+
+    def gemm(name, fn, fl=flop):
+        ms = timed(fn, iters, 3) / iters
+        out[name] = {"ms": ms, "tflops": fl / ms / 1e9}
+
+    for bs in (32, 128):
+        hi, lo, sh, sl = fused_dual_quantize_fp8(w, bs)
+        a, sa = block_quantize_fp8(x, bs)
+        gemm(f"block{bs}_forward", lambda: fused_block_scaled_dual_gemm_forward(a, hi, lo, sa, sh, sl, bs))
+    hi, lo, sh, sl = fused_dual_quantize_fp8(w, 64)
+    a, sa = block_quantize_fp8(x, 64)
+    gq, sg = block_quantize_fp8(gy, 64, torch.float8_e5m2)
+    fused_block_scaled_backward_dx(gq, hi, lo, sg, sh, sl, 64)                       # fills the re-targeting cache
+    gemm("block64_dx_gemm_weight_retargeted", lambda: fused_block_scaled_backward_dx(gq, hi, lo, sg, sh, sl, 64))
+    ms = timed(lambda: block_retarget(hi, lo, sh, sl, 64), iters, 3) / iters
+    out["block64_retarget_pass"] = {"us": ms * 1e3, "gbs": 4.0 * e / ms / 1e6, "note": "once per weight version"}
+    out["block64_dx_total_first_use"] = {"ms": out["block64_dx_gemm_weight_retargeted"]["ms"] + ms}
+    gemm("block64_dx_exact_bf16_route", lambda: fused_block_scaled_backward_dx(gq, hi, lo, sg, sh, sl, 64, exact_bf16=True))
+    xb = block_dequantize_bf16(a, sa, 64)
+    gemm("block64_dw_bf16_head_tail", lambda: bf16_weight_grad(gy, xb), 2.0 * n**3)
+    pa, ia = to_fp8_e4m3(x)
+    pg, ig = to_fp8_e5m2(gy)
+    gemm("per_tensor_dw_fp8", lambda: fp8_weight_grad(pg, pa, ig, ia), 2.0 * n**3)
+    return out
+
+
 def run_train_workload(args) -> None:
-    """``--workload mlp_large`` (benchmark configuration 3: MLP 4096->16384->4096, 32768 tokens, SRR, AdamW) and
-    ``--workload decoder`` (configuration 4: 4 Llama-style layers, d=4096, 32 heads, FFN 11008, 8x4096 tokens, block-64
-    EF), tensor-parallel over the launched ranks.  Prints one JSON line with the step time."""
+    """``--workload mlp|mlp_large|decoder``: one training workload alone, one JSON line."""
     import torch
     import torch.distributed as dist
 
     from tcfp_b200 import _C
-    from tcfp_b200.workloads import build_decoder, build_mlp
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -199,52 +397,24 @@ def run_train_workload(args) -> None:
     _C.load()
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    g = torch.Generator().manual_seed(1004)
-    if args.workload == "mlp_large":
-        d = 4096
-        model = build_mlp(d, 16384, srr=True).to(dev)
-        x = torch.randn(16 * 2048, d, generator=g).to(torch.bfloat16).to(dev)
-        desc = "MLP 4096->16384->4096 GELU, 16x2048 tokens bf16, per-tensor SRR, AdamW, fwd+bwd+step"
-        flop = 3 * 2 * 2 * x.shape[0] * d * 16384 * (5.0 / 6.0) * 2   # fwd dual + dX dual + dW single
-    else:
-        d = 4096
-        model = build_decoder().to(dev)
-        x = torch.randn(8, 4096, d, generator=g).to(torch.bfloat16).to(dev)
-        desc = "4 decoder layers d=4096 h=32 ffn=11008, batch 8 x seq 4096 bf16, block-64 EF, AdamW, fwd+bwd+step"
-        lin = 4 * (4 * d * d + 3 * d * 11008)
-        flop = 2 * x.shape[0] * x.shape[1] * lin * 5.0              # (2 fwd + 2 dX + 1 dW) products
-    target = torch.randn(x.shape, generator=g).to(torch.bfloat16).to(dev)
-    # SRR advances a host-side stream offset (not capturable); with more than one rank the capture of the
-    # NCCL all-reduces did not complete in the one attempt made, so replay is offered on a single GPU only
-    use_graph = args.graph and args.workload == "decoder" and world == 1
-    opt = torch.optim.AdamW(model.parameters(), lr=3e-4, capturable=use_graph)
+    timed = _make_timed(dev, world)
+    with ClockSampler(local) as clk:
+        res = _train_step_extra(args.workload, dev, world, timed, args.steps, sp=args.sp)
+    _C.check_device_status()
+    if rank == 0:
+        print(json.dumps({
+            "metric": "train_step_ms", "value": res["ms_per_step"], "unit": "ms", "n_gpus": world, "steps": args.steps,
+            "warmup": 3, "ms_per_step": res["ms_per_step"], "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
+            "config": {"workload": res["config"], "parallelism": res["parallelism"]}, "detail": res,
+            "clocks": clk.summary()}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
 
-    def eager_step():
-        opt.zero_grad(set_to_none=not use_graph)
-        loss = torch.nn.functional.mse_loss(model(x).float(), target.float())
-        loss.backward()
-        opt.step()
-        return loss
 
-    step = eager_step
-    if use_graph:
-        # the whole step -- quantizers, GEMMs, NCCL all-reduces, AdamW -- captured once and replayed
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            for _ in range(3):
-                eager_step()
-        torch.cuda.current_stream().wait_stream(side)
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            static_loss = eager_step()
-
-        def step():
-            graph.replay()
-            return static_loss
+def _make_timed(dev, world):
+    import torch
+    import torch.distributed as dist
 
     def barrier():
         torch.cuda.synchronize()
@@ -252,54 +422,65 @@ def run_train_workload(args) -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
-        step()
-    barrier()
-    e0 = torch.cuda.Event(enable_timing=True)
-    e1 = torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as clk:
+    def timed(fn, steps, warmup):
+        """Total device milliseconds of ``steps`` calls after ``warmup`` calls;
+        barrier + synchronize on both sides, maximum over the ranks."""
+        for _ in range(warmup):
+            fn()
+        barrier()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(args.steps):
-            loss = step()
+        for _ in range(steps):
+            fn()
         e1.record()
         barrier()
-    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    ms_per_step = float(ms.item()) / args.steps
-    _C.check_device_status()
-    if rank == 0:
-        print(json.dumps({
-            "metric": "train_step_ms", "value": ms_per_step, "unit": "ms", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "strong",
-            "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
-            "config": {"workload": desc, "parallelism": f"tp{world}", "cuda_graph": bool(use_graph)},
-            "linear_tflops_effective": flop / (ms_per_step * 1e-3) / 1e12, "loss": float(loss.item()),
-            "clocks": clk.summary(), "peak_mem_gb": torch.cuda.max_memory_allocated() / 2**30,
-        }), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    return timed
 
 
 def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    rows = 2048
     t0 = time.perf_counter()
-    val, cores, med = _cpu_sample(rows, max(1, min(args.steps, 5)))
-    sample = f"first {rows} of 8192 activation rows per step (a {rows}x8192x8192 dual matmul), median of {max(1, min(args.steps, 5))}"
+    passes, warm = max(1, args.steps), max(0, min(args.warmup, 3))
+    val, cores, times = _cpu_passes(passes, warm)
+    mean_ms = sum(times) / len(times) * 1e3
+    sample = (f"{passes} whole passes of the workload (all 8192 activation rows, an 8192x8192x8192 dual matmul each) "
+              f"after {warm} warm-up passes; value from the mean pass")
     line = {
         "impl": "reference", "metric": "dual_fp8_gemm_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": med * 1e3 * (M / rows), "higher_is_better": True,
+        "steps": passes, "warmup": warm, "ms_per_step": mean_ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "timing": "host wall clock, CPU"},
+        "config": _config(args.gpus),
         "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "note": "CPU restatement of the reference's block-scaled path (its Triton kernels need a GPU); "
-                "dequantize + FP32 dual matmul on all host cores",
-        "wall_s": time.perf_counter() - t0,
+        "timing": "host wall clock around each pass, CPU",
+        "note": "CPU restatement of the reference's block-scaled path (its Triton kernels need a GPU): "
+                "dequantize + FP32 dual matmul on all host cores, operands quantized beforehand",
     }
+    if not args.no_extras:
+        try:
+            import torch
+
+            if torch.cuda.is_available():
+                from tcfp_b200.kernels import block_quantize_fp8, fused_dual_quantize_fp8
+
+                dev = torch.device("cuda", 0)
+                g = torch.Generator().manual_seed(1003)
+                x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(dev)
+                w = (torch.randn(N, K, generator=g) * 0.02).to(dev)
+                w_hi, w_lo, s_hi, s_lo = fused_dual_quantize_fp8(w, BS)
+                a, s_a = block_quantize_fp8(x, BS)
+                line["reference_gpu"] = _reference_gpu(dev, a, s_a, w_hi, w_lo, s_hi, s_lo, x, w, None)
+        except Exception as e:
+            line["reference_gpu"] = {"error": repr(e)[:200]}
+    line["wall_s"] = time.perf_counter() - t0
     print(json.dumps(line), flush=True)
 
 
@@ -308,7 +489,8 @@ def run_ours(args) -> None:
     import torch.distributed as dist
 
     from tcfp_b200 import _C
-    from tcfp_b200.kernels import block_quantize_fp8, fused_block_scaled_dual_gemm_forward, fused_dual_quantize_fp8
+    from tcfp_b200.kernels import (block_dequantize_fp8, block_quantize_fp8, fused_block_scaled_dual_gemm_forward,
+                                   fused_dual_quantize_fp8)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -331,9 +513,10 @@ def run_ours(args) -> None:
     w_hi, w_lo, s_hi, s_lo = fused_dual_quantize_fp8(w, BS, err)
     a, s_a = block_quantize_fp8(x, BS)
     launches_per_step = 1
+    y_dev = torch.empty(M, N, device=dev, dtype=torch.float32)
 
     def step():
-        return fused_block_scaled_dual_gemm_forward(a, w_hi, w_lo, s_a, s_hi, s_lo, BS)
+        return fused_block_scaled_dual_gemm_forward(a, w_hi, w_lo, s_a, s_hi, s_lo, BS, out=y_dev)
 
     from tcfp_b200.host_pipeline import HostStreamedLinear
 
@@ -342,55 +525,57 @@ def run_ours(args) -> None:
     def e2e_step():
         streamed.forward_from_host(x_host, out_host)
 
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed(fn, steps, warmup):
-        for _ in range(warmup):
-            fn()
-        barrier()
-        e0 = torch.cuda.Event(enable_timing=True)
-        e1 = torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            fn()
-        e1.record()
-        barrier()
-        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item())
-
+    timed = _make_timed(dev, world)
     warmup = max(args.warmup, 3)
     with ClockSampler(local) as clk:
         total_ms = timed(step, args.steps, warmup)
     clocks = clk.summary()
+    ms_per_step = total_ms / args.steps
+
+    # the output that was just timed, checked on a row slice against a plain FP32 product of the dequantized operands
+    rows = slice(0, 256)
+    ref = block_dequantize_fp8(a[rows], s_a[:, rows].contiguous(), BS) @ (
+        block_dequantize_fp8(w_hi, s_hi, BS) + block_dequantize_fp8(w_lo, s_lo, BS)).t()
+    rel = float((y_dev[rows] - ref).norm() / ref.norm())
+    del ref
+    if not rel <= 1e-3:
+        raise RuntimeError(f"the timed GEMM output is wrong: relative Frobenius error {rel:.3e} on rows 0..255")
+
+    # sustained: the same launch back to back for at least two seconds, clocks sampled throughout
+    sus_steps = max(args.steps, int(2200.0 / ms_per_step))
+    with ClockSampler(local, period_s=0.01) as clk_s:
+        sus_ms = timed(step, sus_steps, 1) / sus_steps
+    sus_clk = clk_s.summary()
+
     e2e_steps = max(2, min(args.steps, 10))
     e2e_ms = timed(e2e_step, e2e_steps, 2)
     _C.check_device_status()
 
-    ms_per_step = total_ms / args.steps
     value = world * FLOP_PER_STEP / (ms_per_step * 1e-3) / 1e12
     e2e_value = world * FLOP_PER_STEP / (e2e_ms / e2e_steps * 1e-3) / 1e12
     peaks = _peaks()
     fp8_peak = 2.0 * peaks["bf16"]
     per_gpu = value / world
+    traffic, traffic_src = _profiled_traffic()
     line = {
         "metric": "dual_fp8_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "l2": "operands + output = 448 MB per step, larger than the 126 MB L2",
-                   "parallelism": f"column-parallel shards x{world}, no collective" if world > 1 else "single GPU"},
+        "config": _config(world),
         "pct_of_nominal_fp8_peak": per_gpu / 4500.0,
+        "output_check": {"rel_frobenius_vs_fp32_dequantized_product": rel, "rows": 256, "tolerance": 1e-3},
         "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": fp8_peak, "unit": "TFLOP/s",
-                     "frac": per_gpu / fp8_peak, "traffic": 880.0e6,
-                     "traffic_note": "dram__bytes_read + dram__bytes_write per launch, ncu on this same command; algorithmic 448 MB",
+                     "frac": per_gpu / fp8_peak, "traffic": traffic,
+                     "traffic_note": f"mean dram__bytes_read + dram__bytes_write per launch from {traffic_src} "
+                                     "(ncu on this same command); algorithmic 448 MB",
                      "peak_source": f"2 x {peaks['src']} cuBLAS bf16 burst ({peaks['bf16']} TFLOP/s): no FP8 peak was measured; "
                                     "FP8 tensor rate is twice the bf16 rate",
                      "kernel": "dual_gemm_pair_kernel<KIND_MXF8>", "flop_per_launch": FLOP_PER_STEP},
+        "sustained": {"seconds": sus_ms * sus_steps / 1e3, "launches": sus_steps, "ms_per_step": sus_ms,
+                      "tflops": FLOP_PER_STEP / sus_ms / 1e9, "sm_mhz_median": sus_clk["sm_mhz"],
+                      "sm_mhz_min": sus_clk["sm_mhz_min"], "reasons": sus_clk["reasons"], "samples": sus_clk["samples"],
+                      "ms_times_mhz": (sus_ms * sus_clk["sm_mhz"]) if sus_clk["sm_mhz"] else None,
+                      "frac_of_2x_bf16_sustained": FLOP_PER_STEP / sus_ms / 1e9 / (2.0 * peaks["bf16_sustained"])},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 4,
                 "ms_per_step": e2e_ms / e2e_steps,
                 "path": "HostStreamedLinear.forward_from_host: pinned host X -> H2D -> fused_dual_quantize_fp8(W, EF) -> "
@@ -398,15 +583,36 @@ def run_ours(args) -> None:
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks,
     }
-    try:
-        line["extra"] = {"mlp_train_step": _mlp_train_step_ms(world, dev, timed)}
-    except Exception as e:  # the headline line must not depend on the extra measurement
-        line["extra"] = {"mlp_train_step": {"error": repr(e)[:200]}}
+    del streamed, x_host, out_host
+    extra: dict = {}
+    if not args.no_extras:
+        if world == 1:
+            try:
+                extra["reference_gpu"] = _reference_gpu(dev, a, s_a, w_hi, w_lo, s_hi, s_lo, x, w, ms_per_step)
+            except Exception as e:
+                extra["reference_gpu"] = {"error": repr(e)[:200]}
+        del a, s_a, w_hi, w_lo, s_hi, s_lo, x, w, err, y_dev
+        torch.cuda.empty_cache()
+        if world == 1:
+            try:
+                extra["kernels"] = _kernel_extras(dev, timed)
+            except Exception as e:
+                extra["kernels"] = {"error": repr(e)[:200]}
+            torch.cuda.empty_cache()
+        for key, name, steps in (("mlp_train_step", "mlp", 10), ("mlp_large_train_step", "mlp_large", 5),
+                                 ("decoder_train_step", "decoder", 3)):
+            try:  # the headline line must not depend on an extra measurement
+                extra[key] = _train_step_extra(name, dev, world, timed, steps)
+            except Exception as e:
+                extra[key] = {"error": repr(e)[:200]}
+            torch.cuda.empty_cache()
+    line["extra"] = extra
     _C.check_device_status()
     if rank == 0 and world == 1:
-        val, cores, med = _cpu_sample(2048, 3)
+        val, cores, times = _cpu_passes(3, 1)
         line["cpu_baseline"] = {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port",
-                                "sample": "first 2048 of 8192 activation rows (2048x8192x8192 dual matmul), median of 3"}
+                                "sample": "3 whole passes of the workload (8192x8192x8192 dequantize + FP32 dual matmul) "
+                                          "after 1 warm-up pass; value from the mean pass"}
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -419,13 +625,14 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="gemm", choices=["gemm", "mlp_large", "decoder"])
-    ap.add_argument("--graph", action="store_true", help="decoder workload: replay the step from a CUDA graph")
+    ap.add_argument("--workload", default="gemm", choices=["gemm", "mlp", "mlp_large", "decoder"])
+    ap.add_argument("--sp", action="store_true", help="decoder workload: sequence-parallel form")
+    ap.add_argument("--no-extras", action="store_true", help="headline line only")
     args = ap.parse_args()
-    if args.workload != "gemm" and args.impl == "ours":
-        run_train_workload(args)
-    elif args.impl == "reference":
+    if args.impl == "reference":
         run_reference(args)
+    elif args.workload != "gemm":
+        run_train_workload(args)
     else:
         run_ours(args)
 

@@ -228,6 +228,40 @@ int32_t tcfp_block_dual_gemm_static(const uint8_t* a, const int8_t* exp_a,
 size_t tcfp_static_scratch_bytes_per_operand(void);
 
 /*
+ * Block-scaled input gradient on the FP8 tensor-core path, in two steps.
+ *
+ * tcfp_block_retarget: rewrites a block-quantized weight (R = D_out rows,
+ * C = D_in columns; exponents exp_* in the reference layout (C/bs, R)) into the
+ * orientation the backward contraction needs: codes TRANSPOSED to (C, R) and
+ * one exponent per (column c, block of bs rows), written as planes t_* of
+ * shape (R/bs, C) -- the reference layout of an operand with rows = C and
+ * K = R, ready for tcfp_pack_scales.  t = max of the rows' exponents in the
+ * block; each code is re-encoded as value * 2^(s - t).  Exact except where the
+ * down-shift drops below E4M3's subnormal step (absolute error <= 2^-10 * 2^t).
+ * The -128 sentinel of the residual plane contributes zeros.  w_lo and its
+ * three companions may all be NULL.  Depends only on the quantized weight: do
+ * it once per weight version and reuse it across micro-batches.
+ *
+ * tcfp_block_dx_gemm:
+ *   out(M, D_in) = sum_kb 2^sg[kb,m] * (2^t_hi[kb,n] * G_kb.HiT_kb + 2^t_lo[kb,n] * G_kb.LoT_kb)
+ * with G (M, D_out) E5M2 block-quantized along D_out and the retargeted
+ * operands (D_in, D_out); all scale factors as packed chunk arrays.  Together
+ * they replace fused_block_scaled_backward_dx (tcfp/kernels.py:2326-2425,
+ * kernel :1051-1205), which dequantizes to FP32 and multiplies in TF32.
+ */
+int32_t tcfp_block_retarget(const uint8_t* w_hi, const uint8_t* w_lo,
+                            const int8_t* exp_hi, const int8_t* exp_lo,
+                            uint8_t* hi_t, uint8_t* lo_t, int8_t* t_hi,
+                            int8_t* t_lo, int64_t R, int64_t C,
+                            int32_t block_size, void* stream);
+int32_t tcfp_block_dx_gemm(const uint8_t* g, const uint8_t* sf_g,
+                           const uint8_t* w_hi_t, const uint8_t* sf_hi_t,
+                           const uint8_t* w_lo_t, const uint8_t* sf_lo_t,
+                           void* out, int32_t out_dtype, int64_t M,
+                           int64_t d_in, int64_t d_out, int32_t block_size,
+                           void* stream);
+
+/*
  * BF16 dual GEMM on exactly dequantized operands:
  *   trans_b == 1: out(M,N) = A(M,K) . (B_hi(K,N) + B_lo(K,N))   (block dX)
  *   trans_b == 0: out(M,N) = A(M,K) . (B_hi(N,K) + B_lo(N,K))^T

@@ -192,8 +192,20 @@ def dual_quantize_per_tensor(
 # ---------------------------------------------------------------------------
 
 def _block_exponent(amax: torch.Tensor, fmax: float) -> torch.Tensor:
-    # tcfp/kernels.py:250-256 (and :367-370, :387-390)
-    raw = torch.ceil(torch.log2(amax.clamp(min=1e-12) / fmax))
+    """``max(ceil(log2(max(amax, 1e-12) / FP8_MAX)), -126)`` (tcfp/kernels.py:
+    250-256, 367-370, 387-390) as the reference's kernels evaluate it on the
+    GPU.  Triton compiles ``/`` on float32 to the PTX instruction
+    ``div.full.f32`` (not an IEEE division) and ``tl.log2`` to a float32 log2
+    accurate to the last bit.  Measured against the reference's own kernel on
+    a B200 over every amax within -6..+320 ulps of ``1.75 * 2^a`` for
+    a = -34..23 and 200 000 random amax values, for both FP8 maxima: the
+    quotient equals ``amax * float32(1 / FP8_MAX)`` (one rounding of the
+    product with the rounded reciprocal), and the exponent then follows from a
+    correctly rounded float32 log2.  An IEEE division differs from it on amax
+    values 1-20 ulps above ``1.75 * 2^a``, where it moves the exponent by one."""
+    recip = (torch.ones((), dtype=torch.float32) / torch.tensor(fmax, dtype=torch.float32))
+    q = amax.clamp(min=1e-12).float() * recip
+    raw = torch.ceil(torch.log2(q.double()).float())
     return raw.clamp(min=-126.0)
 
 

@@ -42,6 +42,10 @@ _SIGNATURES = {
                                c_int64, c_void_p]),
     "tcfp_block_dual_gemm": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                        c_void_p, c_int32, c_int64, c_int64, c_int64, c_int32, c_void_p]),
+    "tcfp_block_retarget": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                      c_int64, c_int64, c_int32, c_void_p]),
+    "tcfp_block_dx_gemm": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32,
+                                     c_int64, c_int64, c_int64, c_int32, c_void_p]),
     "tcfp_block_dual_gemm_static": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                               c_void_p, c_int32, c_int64, c_int64, c_int64, c_int32, c_void_p]),
     "tcfp_static_scratch_bytes_per_operand": (c_size_t, []),

@@ -22,6 +22,7 @@ COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC"]
 # quantize.cu decides rounding byte-for-byte: never let ptxas contract a*b+c
 UNITS = [
     ("quantize.cu", ["--fmad=false"]),
+    ("retarget.cu", ["--fmad=false"]),
     ("gemm_sm100.cu", []),
     ("gemm2_sm100.cu", []),
     ("noalloc.cu", []),

@@ -57,16 +57,20 @@ __device__ __forceinline__ float clampf(float x, float lim) {
 
 // ---- power-of-two block exponent ------------------------------------------
 // e = max(ceil(log2(max(amax,1e-12) / fmax)), -126)   (tcfp/kernels.py:250-256)
-// where log2 is a float32 log2.  q = amax/fmax = 2^k (1+f):
-//   f == 0            -> e = k
-//   f  > 2^-17        -> e = k+1 (log2(1+f) is far above half an ulp of k)
-//   otherwise the float32 result of log2 may round DOWN to k; decide it the
-//   way a correctly rounded float32 log2 does (double log2, then round).
+// evaluated the way the reference's Triton kernels evaluate it on the GPU:
+// the float32 "/" is the PTX instruction div.full.f32 (an approximate
+// division: for these operands amax * RN(1/fmax), one ulp above the IEEE
+// quotient for many amax), the log2 is the full-precision float32 log2.  Both
+// are issued here as the same operations, so the exponents agree with the
+// reference kernel bit for bit, including amax values a few ulps above
+// fmax * 2^k where an IEEE division would land on the other side of the
+// integer.
+//
 // Fast form for fmax = 1.75 * 2^P (448: P = 8, 57344: P = 15).  With
-// amax = 2^a (1+f): f < 0.75 puts amax/fmax strictly between 2^(a-P-1) and
-// 2^(a-P) with a large mantissa, so e = a-P; f >= 0.75 gives a quotient
-// 2^(a-P) * r with r in [1, 1.143), so e = a-P+1 unless r is within a few
-// ulps of 1 -- that sliver goes through the exact rule below.
+// amax = 2^a (1+f): f < 0.75 puts the quotient in (2^(a-P-1), 2^(a-P)]
+// (the top of that range rounds to 2^(a-P) exactly), so e = a-P;
+// f >= 0.75 + 256 ulps gives a quotient safely above 2^(a-P), so e = a-P+1;
+// the sliver in between goes through the full rule.
 __device__ __forceinline__ int block_exponent(float amax, float fmax);
 template <bool E5M2>
 __device__ __forceinline__ int block_exponent_fast(float amax) {
@@ -82,21 +86,16 @@ __device__ __forceinline__ int block_exponent_fast(float amax) {
   return e < -126 ? -126 : e;
 }
 
+__device__ __forceinline__ float div_full_f32(float a, float b) {
+  float q;
+  asm("div.full.f32 %0, %1, %2;" : "=f"(q) : "f"(a), "f"(b));
+  return q;
+}
+
 __device__ __forceinline__ int block_exponent(float amax, float fmax) {
   amax = fmaxf(amax, kAmaxFloor);
-  float q = __fdiv_rn(amax, fmax);
-  uint32_t b = __float_as_uint(q);
-  int k = (int)((b >> 23) & 0xFF) - 127;
-  uint32_t mant = b & 0x7FFFFFu;
-  int e;
-  if (mant == 0) {
-    e = k;
-  } else if (mant >= 64u) {
-    e = k + 1;
-  } else {
-    float lf = (float)log2((double)q);
-    e = (int)ceilf(lf);
-  }
+  const float q = div_full_f32(amax, fmax);
+  const int e = (int)ceilf(log2f(q));
   return e < -126 ? -126 : e;
 }
 

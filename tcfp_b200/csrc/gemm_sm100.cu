@@ -575,32 +575,48 @@ extern "C" int32_t tcfp_dw_gemm(const uint8_t* g, int32_t g_fmt, const uint8_t* 
                                 : launch<KIND_F8, true, false, true>(g, x, nullptr, out, p, stream);
 }
 
-extern "C" int32_t tcfp_block_dual_gemm(const uint8_t* a, const uint8_t* sf_a, const uint8_t* w_hi,
-                                        const uint8_t* sf_hi, const uint8_t* w_lo, const uint8_t* sf_lo,
-                                        const float* bias, void* out, int32_t out_dtype, int64_t M, int64_t N,
-                                        int64_t K, int32_t block_size, void* stream_) {
-  cudaStream_t stream = (cudaStream_t)stream_;
-  if (!a || !sf_a || !w_hi || !sf_hi || !out) return fail(TCFP_ERR_INVALID, "block_dual_gemm: NULL pointer");
-  if ((w_lo == nullptr) != (sf_lo == nullptr)) return fail(TCFP_ERR_INVALID, "block_dual_gemm: w_lo and sf_lo go together");
+namespace {
+int block_dual_gemm_impl(const char* who, const uint8_t* a, int a_fmt, const uint8_t* sf_a, const uint8_t* w_hi,
+                         const uint8_t* sf_hi, const uint8_t* w_lo, const uint8_t* sf_lo, const float* bias, void* out,
+                         int32_t out_dtype, int64_t M, int64_t N, int64_t K, int32_t block_size, cudaStream_t stream) {
+  if (!a || !sf_a || !w_hi || !sf_hi || !out) return fail(TCFP_ERR_INVALID, "%s: NULL pointer", who);
+  if ((w_lo == nullptr) != (sf_lo == nullptr)) return fail(TCFP_ERR_INVALID, "%s: w_lo and sf_lo go together", who);
   if (block_size != 32 && block_size != 64 && block_size != 128)
     return fail(TCFP_ERR_INVALID, "block_size must be 32, 64, or 128, got %d", block_size);
-  if (out_dtype != TCFP_F32 && out_dtype != TCFP_BF16) return fail(TCFP_ERR_INVALID, "block_dual_gemm: output must be float32 or bfloat16");
-  int rc = check_dims("block_dual_gemm", M, N, K);
+  if (out_dtype != TCFP_F32 && out_dtype != TCFP_BF16) return fail(TCFP_ERR_INVALID, "%s: output must be float32 or bfloat16", who);
+  int rc = check_dims(who, M, N, K);
   if (rc != TCFP_OK) return rc;
   if (K % block_size != 0) return fail(TCFP_ERR_INVALID, "K (%lld) must be divisible by block_size (%d)", (long long)K, block_size);
   if (((uintptr_t)sf_a | (uintptr_t)sf_hi | (uintptr_t)sf_lo) & 15u)
-    return fail(TCFP_ERR_INVALID, "block_dual_gemm: scale-factor arrays must be 16-byte aligned");
+    return fail(TCFP_ERR_INVALID, "%s: scale-factor arrays must be 16-byte aligned", who);
   GemmParams p{};
   p.M = (int)M; p.N = (int)N; p.K = (int)K;
-  p.a_fmt = TCFP_E4M3;
+  p.a_fmt = a_fmt;
   p.block_size = block_size;
   p.bias = bias;
   p.sf_a = sf_a; p.sf_hi = sf_hi; p.sf_lo = sf_lo;
   if (use_pair_kernel(M))
     return pair_gemm_dispatch(KIND_MXF8, false, false, out_dtype == TCFP_BF16, a, w_hi, w_lo, sf_a, sf_hi, sf_lo, out, (int)M,
-                              (int)N, (int)K, TCFP_E4M3, block_size, nullptr, nullptr, nullptr, bias, stream);
+                              (int)N, (int)K, a_fmt, block_size, nullptr, nullptr, nullptr, bias, stream);
   return out_dtype == TCFP_BF16 ? launch<KIND_MXF8, false, true>(a, w_hi, w_lo, out, p, stream)
                                 : launch<KIND_MXF8, false, false>(a, w_hi, w_lo, out, p, stream);
+}
+}  // namespace
+
+extern "C" int32_t tcfp_block_dual_gemm(const uint8_t* a, const uint8_t* sf_a, const uint8_t* w_hi,
+                                        const uint8_t* sf_hi, const uint8_t* w_lo, const uint8_t* sf_lo,
+                                        const float* bias, void* out, int32_t out_dtype, int64_t M, int64_t N,
+                                        int64_t K, int32_t block_size, void* stream_) {
+  return block_dual_gemm_impl("block_dual_gemm", a, TCFP_E4M3, sf_a, w_hi, sf_hi, w_lo, sf_lo, bias, out, out_dtype, M, N, K,
+                              block_size, (cudaStream_t)stream_);
+}
+
+extern "C" int32_t tcfp_block_dx_gemm(const uint8_t* g, const uint8_t* sf_g, const uint8_t* w_hi_t,
+                                      const uint8_t* sf_hi_t, const uint8_t* w_lo_t, const uint8_t* sf_lo_t, void* out,
+                                      int32_t out_dtype, int64_t M, int64_t d_in, int64_t d_out, int32_t block_size,
+                                      void* stream_) {
+  return block_dual_gemm_impl("block_dx_gemm", g, TCFP_E5M2, sf_g, w_hi_t, sf_hi_t, w_lo_t, sf_lo_t, nullptr, out, out_dtype,
+                              M, d_in, d_out, block_size, (cudaStream_t)stream_);
 }
 
 extern "C" int32_t tcfp_bf16_dw_gemm(const void* x, const void* g_hi, const void* g_lo, void* out, int32_t out_dtype,

@@ -59,11 +59,29 @@ def _alloc_sf(rows: int, K: int, bs: int, device) -> torch.Tensor:
     return torch.empty(n, dtype=torch.uint8, device=device)
 
 
+def packed_scale_rows(sf: torch.Tensor, r0: int, r1: int, K: int, block_size: int) -> torch.Tensor:
+    """The part of a packed scale-factor array that covers rows ``[r0, r1)``
+    of its operand (``r0`` a multiple of 128: chunks hold 128 rows each)."""
+    assert r0 % 128 == 0, "row slices of packed scale factors start on multiples of 128"
+    per_row_block = ((K // block_size + 3) // 4) * 512
+    return sf[(r0 // 128) * per_row_block:((r1 + 127) // 128) * per_row_block]
+
+
+def _attach_sf(exps: torch.Tensor, sf: torch.Tensor, block_size: int) -> None:
+    # the packed copy is only valid for the bytes it was packed from: remember the plane's
+    # version counter and address so that an in-place edit or a re-bound storage repacks
+    exps._tcfp_sf = (sf, exps._version, exps.data_ptr(), block_size)
+
+
 def pack_block_scales(exps: torch.Tensor, block_size: int) -> torch.Tensor:
-    """int8 exponent plane ``(K // bs, rows)`` -> packed E8M0 chunk array."""
+    """int8 exponent plane ``(K // bs, rows)`` -> packed E8M0 chunk array.
+    A quantizer of this module attaches the packed copy it wrote in the same
+    pass; it is reused only while the plane is unmodified."""
     cached = getattr(exps, "_tcfp_sf", None)
     if cached is not None:
-        return cached
+        sf, version, addr, bs = cached
+        if version == exps._version and addr == exps.data_ptr() and bs == block_size:
+            return sf
     assert exps.dtype == torch.int8 and exps.ndim == 2 and exps.is_contiguous()
     num_kb, rows = exps.shape
     K = num_kb * block_size
@@ -77,7 +95,7 @@ def pack_block_scales(exps: torch.Tensor, block_size: int) -> torch.Tensor:
 # ---------------------------------------------------------------------------
 
 def fused_dual_gemm_forward(act_fp8, w_hi_fp8, w_lo_fp8, act_inv, w_hi_inv, w_lo_inv, *,
-                            bias=None, out_dtype=torch.float32):
+                            bias=None, out_dtype=torch.float32, out=None):
     """``(act @ W_hi.T) * s + (act @ W_lo.T) * s`` -> ``(M, N)``
     (tcfp/kernels.py:1545-1601).  ``w_lo_fp8`` / ``w_lo_inv`` may be ``None``."""
     M, K = act_fp8.shape
@@ -86,7 +104,10 @@ def fused_dual_gemm_forward(act_fp8, w_hi_fp8, w_lo_fp8, act_inv, w_hi_inv, w_lo
         f"Shape mismatch: act({M},{K}), w_hi({N},{K2}), w_lo{None if w_lo_fp8 is None else tuple(w_lo_fp8.shape)}"
     )
     assert act_fp8.is_contiguous() and w_hi_fp8.is_contiguous(), "operands must be contiguous"
-    out = torch.empty((M, N), device=act_fp8.device, dtype=out_dtype)
+    if out is None:
+        out = torch.empty((M, N), device=act_fp8.device, dtype=out_dtype)
+    else:
+        assert out.shape == (M, N) and out.dtype == out_dtype and out.is_contiguous(), "bad out buffer"
     _C.check(_C.load().tcfp_dual_gemm(
         _C.ptr(act_fp8), _fmt(act_fp8), _C.ptr(w_hi_fp8), _C.ptr(w_lo_fp8),
         _C.ptr(_scalar(act_inv)), _C.ptr(_scalar(w_hi_inv)), _C.ptr(None if w_lo_inv is None else _scalar(w_lo_inv)),
@@ -173,7 +194,7 @@ def block_quantize_fp8(tensor, block_size=128, fp8_dtype=torch.float8_e4m3fn, *,
     _C.check(_C.load().tcfp_quantize(
         _C.ptr(tensor), _C.dtype_code(tensor), _C.ptr(out), _C.ptr(scales), _C.ptr(sf), _C.ptr(deq),
         M, K, block_size, _fmt(out), None, None, 0, 0, 0, None, _C.stream()))
-    scales._tcfp_sf = sf
+    _attach_sf(scales, sf, block_size)
     if want_bf16:
         return out, scales, deq
     return out, scales
@@ -249,8 +270,8 @@ def fused_dual_quantize_fp8(weight, block_size=128, error_buf=None, stochastic_l
         _C.ptr(weight), _C.dtype_code(weight), _C.ptr(error_buf), _C.ptr(w_hi), _C.ptr(w_lo),
         _C.ptr(scales_hi), _C.ptr(scales_lo), _C.ptr(sf_hi), _C.ptr(sf_lo), N, K, block_size, mode,
         int(seed or 0), int(offset), None, None, None, None, _C.stream()))
-    scales_hi._tcfp_sf = sf_hi
-    scales_lo._tcfp_sf = sf_lo
+    _attach_sf(scales_hi, sf_hi, block_size)
+    _attach_sf(scales_lo, sf_lo, block_size)
     return w_hi, w_lo, scales_hi, scales_lo
 
 
@@ -260,17 +281,19 @@ def fused_dual_quantize_fp8(weight, block_size=128, error_buf=None, stochastic_l
 
 def fused_block_scaled_dual_gemm_forward(act_fp8, w_hi_fp8, w_lo_fp8, act_scales, w_hi_scales, w_lo_scales,
                                          block_size, sparse_threshold=0.0, persistent=True, launch_mult=1, *,
-                                         bias=None, out_dtype=torch.float32, out=None):
+                                         bias=None, out_dtype=torch.float32, out=None, act_sf=None):
     """Block-scaled 2-GEMM forward (tcfp/kernels.py:1939-2028).  The tuning
     arguments of the reference are accepted and ignored: the kernel is always
-    persistent with one CTA per SM."""
+    persistent with one CTA per SM.  ``act_sf`` passes the packed activation
+    scale factors explicitly (a row slice of a larger operand's array);
+    ``act_scales`` is then not consulted."""
     M, K = act_fp8.shape
     N, K2 = w_hi_fp8.shape
     assert K == K2 and (w_lo_fp8 is None or w_lo_fp8.shape == (N, K)), (
         f"Shape mismatch: act({M},{K}), w_hi({N},{K2})"
     )
     assert K % block_size == 0, f"K ({K}) must be divisible by block_size ({block_size})"
-    sf_a = pack_block_scales(act_scales, block_size)
+    sf_a = act_sf if act_sf is not None else pack_block_scales(act_scales, block_size)
     sf_hi = pack_block_scales(w_hi_scales, block_size)
     sf_lo = pack_block_scales(w_lo_scales, block_size) if w_lo_fp8 is not None else None
     if out is None:
@@ -311,11 +334,57 @@ def fused_act_quant_dual_gemm_forward(act, w_hi_fp8, w_lo_fp8, w_hi_scales, w_lo
     return out, None, None
 
 
+def block_retarget(w_hi_fp8, w_lo_fp8, w_hi_scales, w_lo_scales, block_size):
+    """One launch of ``tcfp_block_retarget``: ``(hi_t, lo_t, t_hi, t_lo)`` with
+    the codes transposed to ``(D_in, D_out)`` and int8 exponent planes
+    ``(D_out // bs, D_in)``; ``lo`` entries ``None`` without ``w_lo_fp8``."""
+    D_out, D_in = w_hi_fp8.shape
+    assert w_hi_fp8.is_contiguous() and w_hi_scales.is_contiguous(), "operands must be contiguous"
+    assert w_hi_scales.shape == (D_in // block_size, D_out), "scales must be (D_in // block_size, D_out)"
+    dev = w_hi_fp8.device
+    hi_t = torch.empty((D_in, D_out), device=dev, dtype=torch.float8_e4m3fn)
+    t_hi = torch.empty((D_out // block_size, D_in), device=dev, dtype=torch.int8)
+    lo_t = t_lo = None
+    if w_lo_fp8 is not None:
+        assert w_lo_fp8.is_contiguous() and w_lo_scales.is_contiguous(), "operands must be contiguous"
+        lo_t = torch.empty((D_in, D_out), device=dev, dtype=torch.float8_e4m3fn)
+        t_lo = torch.empty((D_out // block_size, D_in), device=dev, dtype=torch.int8)
+    _C.check(_C.load().tcfp_block_retarget(
+        _C.ptr(w_hi_fp8), _C.ptr(w_lo_fp8), _C.ptr(w_hi_scales), _C.ptr(w_lo_scales), _C.ptr(hi_t), _C.ptr(lo_t),
+        _C.ptr(t_hi), _C.ptr(t_lo), D_out, D_in, block_size, _C.stream()))
+    return hi_t, lo_t, t_hi, t_lo
+
+
+def retarget_block_weights(w_hi_fp8, w_lo_fp8, w_hi_scales, w_lo_scales, block_size):
+    """Quantized weight ``(D_out, D_in)`` with scales along ``D_in`` -> the
+    operands of the input-gradient GEMM: codes transposed to ``(D_in, D_out)``
+    and scale factors along ``D_out`` (``tcfp_block_retarget``).  Returns
+    ``(hi_t, lo_t, sf_hi_t, sf_lo_t)`` (``lo`` entries ``None`` without
+    ``w_lo_fp8``).  The result depends only on the quantized weight; it is
+    kept on ``w_hi_fp8`` and reused while none of the four inputs changes, so
+    gradient-accumulation micro-batches pay for it once."""
+    D_out, D_in = w_hi_fp8.shape
+    key = (w_hi_fp8._version, w_hi_scales._version, w_hi_scales.data_ptr(), block_size,
+           None if w_lo_fp8 is None else (w_lo_fp8.data_ptr(), w_lo_fp8._version, w_lo_scales._version))
+    cached = getattr(w_hi_fp8, "_tcfp_dx", None)
+    if cached is not None and cached[0] == key:
+        return cached[1]
+    hi_t, lo_t, t_hi, t_lo = block_retarget(w_hi_fp8, w_lo_fp8, w_hi_scales, w_lo_scales, block_size)
+    out = (hi_t, lo_t, pack_block_scales(t_hi, block_size), None if t_lo is None else pack_block_scales(t_lo, block_size))
+    w_hi_fp8._tcfp_dx = (key, out)
+    return out
+
+
 def fused_block_scaled_backward_dx(grad_fp8, w_hi_fp8, w_lo_fp8, grad_scales, w_hi_scales, w_lo_scales, block_size,
-                                   persistent=True, launch_mult=1, *, grad_bf16=None, out_dtype=torch.float32):
-    """Block-scaled dX (tcfp/kernels.py:2326-2425).  The weight scales vary
-    along the contraction axis here, so the operands are dequantized to bf16
-    (exact) and multiplied on the bf16 tensor-core path."""
+                                   persistent=True, launch_mult=1, *, out_dtype=torch.float32, exact_bf16=False,
+                                   grad_bf16=None):
+    """Block-scaled dX ``(M, D_in)`` (tcfp/kernels.py:2326-2425).  The weight
+    scales run along ``D_in`` but dX contracts over ``D_out``: the quantized
+    weight is re-targeted once per weight version (:func:`retarget_block_weights`)
+    and the product runs on the FP8 block-scaled tensor-core path, like the
+    forward.  ``exact_bf16=True`` takes the other route: every operand is
+    dequantized to bf16 (exact) and multiplied on the bf16 tensor-core path at
+    half the rate."""
     M, D_out = grad_fp8.shape
     D_out2, D_in = w_hi_fp8.shape
     assert D_out == D_out2 and (w_lo_fp8 is None or w_lo_fp8.shape == (D_out, D_in)), (
@@ -323,14 +392,24 @@ def fused_block_scaled_backward_dx(grad_fp8, w_hi_fp8, w_lo_fp8, grad_scales, w_
     )
     assert D_out % block_size == 0, f"D_out={D_out} must be divisible by block_size={block_size}"
     assert D_in % block_size == 0, f"D_in={D_in} must be divisible by block_size={block_size}"
-    if grad_bf16 is None:
-        grad_bf16 = block_dequantize_bf16(grad_fp8, grad_scales, block_size)
-    hi = block_dequantize_bf16(w_hi_fp8, w_hi_scales, block_size)
-    lo = block_dequantize_bf16(w_lo_fp8, w_lo_scales, block_size, sentinel_zero=True) if w_lo_fp8 is not None else None
     out = torch.empty((M, D_in), device=grad_fp8.device, dtype=out_dtype)
-    _C.check(_C.load().tcfp_bf16_dual_gemm(
-        _C.ptr(grad_bf16), _C.ptr(hi), _C.ptr(lo), None, _C.ptr(out), _out_code(out_dtype),
-        M, D_in, D_out, 1, _C.stream()))
+    if exact_bf16:
+        if grad_bf16 is None:
+            grad_bf16 = block_dequantize_bf16(grad_fp8, grad_scales, block_size)
+        hi = block_dequantize_bf16(w_hi_fp8, w_hi_scales, block_size)
+        lo = None
+        if w_lo_fp8 is not None:
+            lo = block_dequantize_bf16(w_lo_fp8, w_lo_scales, block_size, sentinel_zero=True)
+        _C.check(_C.load().tcfp_bf16_dual_gemm(
+            _C.ptr(grad_bf16), _C.ptr(hi), _C.ptr(lo), None, _C.ptr(out), _out_code(out_dtype),
+            M, D_in, D_out, 1, _C.stream()))
+        return out
+    assert grad_fp8.dtype == torch.float8_e5m2 and grad_fp8.is_contiguous(), "gradient codes must be contiguous E5M2"
+    hi_t, lo_t, sf_hi_t, sf_lo_t = retarget_block_weights(w_hi_fp8, w_lo_fp8, w_hi_scales, w_lo_scales, block_size)
+    sf_g = pack_block_scales(grad_scales, block_size)
+    _C.check(_C.load().tcfp_block_dx_gemm(
+        _C.ptr(grad_fp8), _C.ptr(sf_g), _C.ptr(hi_t), _C.ptr(sf_hi_t), _C.ptr(lo_t), _C.ptr(sf_lo_t), _C.ptr(out),
+        _out_code(out_dtype), M, D_in, D_out, block_size, _C.stream()))
     return out
 
 

@@ -37,6 +37,8 @@ from .kernels import (
     fused_dual_gemm_backward_dx,
     fused_dual_gemm_forward,
     fused_dual_quantize_fp8,
+    pack_block_scales,
+    packed_scale_rows,
 )
 
 
@@ -57,6 +59,64 @@ def _master(weight: torch.Tensor) -> torch.Tensor:
     return w.contiguous()
 
 
+class LayerHooks:
+    """Communication hooks a tensor-parallel wrapper installs on a layer
+    (``TCFPLinear._hooks``); the autograd Functions call them at the points
+    where a collective can overlap the layer's own GEMMs.
+
+    ``out_hook(chunk)`` is called with each finished row chunk of the forward
+    output (``row_chunks`` of them, on 128-row boundaries) and may start an
+    asynchronous in-place reduction of it; ``dx_hook(grad_input)`` is called
+    with the input gradient before the weight gradient is computed.  Both
+    return ``None`` or an object whose ``wait()`` makes the current stream
+    wait for the collective."""
+
+    def __init__(self, out_hook=None, row_chunks: int = 1, dx_hook=None):
+        self.out_hook = out_hook
+        self.row_chunks = max(1, int(row_chunks))
+        self.dx_hook = dx_hook
+
+
+def _row_chunks(M: int, hooks) -> list[tuple[int, int]]:
+    if hooks is None or hooks.out_hook is None:
+        return [(0, M)]
+    rows = -(-M // hooks.row_chunks)
+    rows = max(128, -(-rows // 128) * 128)
+    return [(r0, min(M, r0 + rows)) for r0 in range(0, M, rows)]
+
+
+def _wait_all(pending) -> None:
+    for h in pending:
+        if h is not None:
+            h.wait()
+
+
+def _cached_quantize(cache: dict | None, w: torch.Tensor, error_buf, update_ef: bool, srr: bool, tag, quantize):
+    """Weight quantization reused across forwards that must produce the same
+    bytes.  The reference re-quantizes on every forward (tcfp/nn/__init__.py:
+    344-372, 627-632); between two optimizer steps -- gradient-accumulation
+    micro-batches, checkpoint recomputation -- the weight and the error buffer
+    do not change, so every forward after the one that updated the buffer
+    quantizes the same ``W + e`` to the same codes.  Those are kept on the
+    layer, keyed on the weight's and the buffer's version counters and
+    addresses.  Not used for the stochastic residual (fresh randoms per
+    forward), for a forward that updates the error buffer, or while a CUDA
+    graph is being captured (a replayed step must quantize the weight it finds)."""
+    reusable = (cache is not None and not srr and (error_buf is None or not update_ef)
+                and not torch.cuda.is_current_stream_capturing())
+    if not reusable:
+        if cache is not None:
+            cache.clear()
+        return quantize()
+    key = (tag, w.data_ptr(), w._version, tuple(w.shape), w.dtype,
+           None if error_buf is None else (error_buf.data_ptr(), error_buf._version))
+    if cache.get("key") == key:
+        return cache["value"]
+    value = quantize()
+    cache["key"], cache["value"] = key, value
+    return value
+
+
 # ---------------------------------------------------------------------------
 # per-tensor scaling (tcfp/nn/__init__.py:312-566)
 # ---------------------------------------------------------------------------
@@ -66,7 +126,7 @@ class _TCFP12TensorCoreFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, input, weight, bias, hp_grad_weight, error_state, param_name, delayed_scaling, abd, srr,
-                update_ef, srr_seed, srr_offset, out_dtype=torch.float32, nf_sigma=None):
+                update_ef, srr_seed, srr_offset, out_dtype=torch.float32, nf_sigma=None, wq_cache=None, hooks=None):
         w = _master(weight)
         error_buf = None
         if error_state is not None:
@@ -103,15 +163,26 @@ class _TCFP12TensorCoreFunction(torch.autograd.Function):
                 w_hi, w_lo, inv_hi, inv_lo, _ = dual_quantize_per_tensor(
                     w, error_buf, update_error=update_ef, amax_hi=delayed, amax_lo=predicted)
         else:
-            w_hi, w_lo, inv_hi, inv_lo, _ = dual_quantize_per_tensor(
-                w, error_buf, srr=srr, update_error=update_ef, seed=srr_seed, offset=srr_offset)
+            w_hi, w_lo, inv_hi, inv_lo, _ = _cached_quantize(
+                wq_cache, w, error_buf, update_ef, srr, "per_tensor",
+                lambda: dual_quantize_per_tensor(w, error_buf, srr=srr, update_error=update_ef, seed=srr_seed,
+                                                 offset=srr_offset))
+        if wq_cache is not None and (nf_sigma is not None or (delayed_scaling and error_state is not None)):
+            wq_cache.clear()       # these modes advance scaling state on every forward: nothing to reuse
 
         input_shape = input.shape
         x2d = _flat2d(input)
         act_fp8, act_inv = to_fp8_e4m3(x2d)                      # always fresh (:390)
-        out2d = fused_dual_gemm_forward(act_fp8, w_hi, w_lo, act_inv, inv_hi, inv_lo,
-                                        bias=None if bias is None else bias.detach().float().contiguous(),
-                                        out_dtype=out_dtype)
+        bias_f = None if bias is None else bias.detach().float().contiguous()
+        out2d = torch.empty((x2d.shape[0], w_hi.shape[0]), device=x2d.device, dtype=out_dtype)
+        pending = []
+        for r0, r1 in _row_chunks(x2d.shape[0], hooks):
+            fused_dual_gemm_forward(act_fp8[r0:r1], w_hi, w_lo, act_inv, inv_hi, inv_lo, bias=bias_f,
+                                    out_dtype=out_dtype, out=out2d[r0:r1])
+            if hooks is not None and hooks.out_hook is not None:
+                pending.append(hooks.out_hook(out2d[r0:r1]))
+        _wait_all(pending)
+        ctx.dx_hook = None if hooks is None else hooks.dx_hook
         ctx.dx_dtype = _dx_dtype(input)
         ctx.hp_grad_weight = hp_grad_weight
         ctx.input_shape = input_shape
@@ -138,6 +209,7 @@ class _TCFP12TensorCoreFunction(torch.autograd.Function):
         grad_fp8, grad_inv = to_fp8_e5m2(g2d)                    # always fresh (:494)
         grad_input = fused_dual_gemm_backward_dx(grad_fp8, w_hi, w_lo, grad_inv, inv_hi, inv_lo,
                                                  out_dtype=ctx.dx_dtype)
+        dx_pending = ctx.dx_hook(grad_input) if ctx.dx_hook is not None else None   # overlaps the dW GEMM below
         grad_input = grad_input.reshape(ctx.input_shape)
         if ctx.hp_grad_weight:
             if saved_act.dtype == torch.bfloat16 and g2d.shape[1] % 16 == 0 and saved_act.shape[1] % 16 == 0:
@@ -147,7 +219,8 @@ class _TCFP12TensorCoreFunction(torch.autograd.Function):
         else:
             grad_weight = fp8_weight_grad(grad_fp8, saved_act, grad_inv, act_inv)   # (:546-555)
         grad_bias = g2d.float().sum(dim=0) if ctx.has_bias else None
-        return (grad_input, grad_weight, grad_bias) + (None,) * 11
+        _wait_all([dx_pending])
+        return (grad_input, grad_weight, grad_bias) + (None,) * 13
 
 
 # ---------------------------------------------------------------------------
@@ -159,7 +232,7 @@ class _TCFP12BlockScaledFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, input, weight, bias, scale_block_size, hp_grad_weight, error_state, param_name, abd, srr,
-                update_ef, srr_seed, srr_offset, out_dtype=torch.float32):
+                update_ef, srr_seed, srr_offset, out_dtype=torch.float32, wq_cache=None, hooks=None):
         w = _master(weight)
         error_buf = None
         if error_state is not None:
@@ -168,16 +241,28 @@ class _TCFP12BlockScaledFunction(torch.autograd.Function):
         # update_ef False (gradient accumulation, checkpoint recomputation):
         # the kernel reads the buffer and leaves it alone -- the reference
         # clones it for the same effect (:607-608)
-        w_hi, w_lo, s_hi, s_lo = fused_dual_quantize_fp8(
-            w, bs, error_buf, srr, seed=srr_seed, offset=srr_offset, update_error=update_ef)
+        w_hi, w_lo, s_hi, s_lo = _cached_quantize(
+            wq_cache, w, error_buf, update_ef, srr, ("block", bs),
+            lambda: fused_dual_quantize_fp8(w, bs, error_buf, srr, seed=srr_seed, offset=srr_offset,
+                                            update_error=update_ef))
         input_shape = input.shape
         x2d = _flat2d(input)
         if x2d.dtype not in (torch.float32, torch.bfloat16):
             x2d = x2d.float()
         act_fp8, act_scales = block_quantize_fp8(x2d, bs, torch.float8_e4m3fn)
-        out2d = fused_block_scaled_dual_gemm_forward(
-            act_fp8, w_hi, w_lo, act_scales, s_hi, s_lo, bs,
-            bias=None if bias is None else bias.detach().float().contiguous(), out_dtype=out_dtype)
+        bias_f = None if bias is None else bias.detach().float().contiguous()
+        M, K = x2d.shape
+        out2d = torch.empty((M, w_hi.shape[0]), device=x2d.device, dtype=out_dtype)
+        act_sf = pack_block_scales(act_scales, bs)
+        pending = []
+        for r0, r1 in _row_chunks(M, hooks):
+            fused_block_scaled_dual_gemm_forward(
+                act_fp8[r0:r1], w_hi, w_lo, act_scales, s_hi, s_lo, bs, bias=bias_f, out_dtype=out_dtype,
+                out=out2d[r0:r1], act_sf=packed_scale_rows(act_sf, r0, r1, K, bs))
+            if hooks is not None and hooks.out_hook is not None:
+                pending.append(hooks.out_hook(out2d[r0:r1]))
+        _wait_all(pending)
+        ctx.dx_hook = None if hooks is None else hooks.dx_hook
         ctx.dx_dtype = _dx_dtype(input)
         ctx.hp_grad_weight = hp_grad_weight
         ctx.input_shape = input_shape
@@ -208,11 +293,13 @@ class _TCFP12BlockScaledFunction(torch.autograd.Function):
         g2d = _flat2d(grad_output)
         if g2d.dtype not in (torch.float32, torch.bfloat16):
             g2d = g2d.float()
-        # E5M2 block quantize of the gradient along D_out (:724-726); the same
-        # pass emits the dequantized bf16 copy the dX GEMM consumes
-        grad_fp8, grad_scales, grad_bf16 = block_quantize_fp8(g2d, bs, torch.float8_e5m2, want_bf16=True)
+        # E5M2 block quantize of the gradient along D_out (:724-726); dX on the FP8 block-scaled MMA against
+        # the weight re-targeted for this contraction (once per weight version, kept on w_hi)
+        grad_fp8, grad_scales = block_quantize_fp8(g2d, bs, torch.float8_e5m2)
         grad_input = fused_block_scaled_backward_dx(grad_fp8, w_hi, w_lo, grad_scales, s_hi, s_lo, bs,
-                                                    grad_bf16=grad_bf16, out_dtype=ctx.dx_dtype).reshape(ctx.input_shape)
+                                                    out_dtype=ctx.dx_dtype)
+        dx_pending = ctx.dx_hook(grad_input) if ctx.dx_hook is not None else None   # overlaps the dW GEMM below
+        grad_input = grad_input.reshape(ctx.input_shape)
         # dW in full precision, as in the reference (:744-750)
         if ctx.hp_grad_weight:
             if saved_act.dtype == torch.bfloat16:
@@ -223,7 +310,8 @@ class _TCFP12BlockScaledFunction(torch.autograd.Function):
             # the saved codes dequantize exactly to bf16; the FP32 gradient goes in as bf16 head + tail
             grad_weight = bf16_weight_grad(g2d, block_dequantize_bf16(saved_act, act_scales, bs))
         grad_bias = g2d.float().sum(dim=0) if ctx.has_bias else None
-        return (grad_input, grad_weight, grad_bias) + (None,) * 10
+        _wait_all([dx_pending])
+        return (grad_input, grad_weight, grad_bias) + (None,) * 12
 
 
 # ---------------------------------------------------------------------------
@@ -317,6 +405,10 @@ class TCFPLinear(nn.Module):
         self._param_name: str = ""
         self._last_weight_version: int = -1
         self._bf16_fallback: bool = False
+        # quantized weight of the last forward that did not update the error buffer (see _cached_quantize)
+        self._wq_cache: dict = {}
+        # communication hooks installed by the tensor-parallel wrappers (LayerHooks) or None
+        self._hooks = None
 
         kw = {"device": device, "dtype": dtype}
         self.weight = nn.Parameter(torch.empty(out_features, in_features, **kw))
@@ -366,11 +458,11 @@ class TCFPLinear(nn.Module):
         if self.mode == TCFPMode.TCFP12 and self.scale_block_size is not None:
             return _TCFP12BlockScaledFunction.apply(
                 x, self.weight, self.bias, self.scale_block_size, self.hp_grad_weight, self._error_state,
-                self._param_name, self.abd, srr, update_ef, self.srr_seed, srr_offset, self.out_dtype)
+                self._param_name, self.abd, srr, update_ef, self.srr_seed, srr_offset, self.out_dtype, self._wq_cache, self._hooks)
         return _TCFP12TensorCoreFunction.apply(
             x, self.weight, self.bias, self.hp_grad_weight, self._error_state, self._param_name,
             self.delayed_scaling, self.abd, srr, update_ef, self.srr_seed, srr_offset, self.out_dtype,
-            self.sigma_factor if self.nf_aware_scaling else None)
+            self.sigma_factor if self.nf_aware_scaling else None, self._wq_cache, self._hooks)
 
     def extra_repr(self) -> str:
         parts = [f"in_features={self.in_features}", f"out_features={self.out_features}",
@@ -400,41 +492,63 @@ class TCFPLinear(nn.Module):
         return ", ".join(parts)
 
 
-def convert_to_tcfp(model: nn.Module, mode: TCFPMode = TCFPMode.TCFP12, block_size: int = DEFAULT_BLOCK_SIZE, *,
-                    skip_patterns: tuple[str, ...] = ("head",), use_tensor_cores: bool = True,
-                    hp_grad_weight: bool = False, error_feedback: bool = True, delayed_scaling: bool = False,
+def convert_to_tcfp(model: nn.Module, mode: TCFPMode = TCFPMode.TCFP12, block_size: int = DEFAULT_BLOCK_SIZE,
+                    skip_patterns: tuple[str, ...] = ("head",), *, nf4_residual: bool = False,
+                    nf_aware_scaling: bool = False, stochastic_rounding: bool = False, warmup_steps: int = 0,
+                    use_tensor_cores: bool = False, hp_grad_weight: bool = False, error_feedback: bool = True,
+                    delayed_scaling: bool = False, use_fused_kernel: bool = True, use_cuda_ext: bool = True,
                     scale_block_size: int | None = None, abd: bool = False, srr: bool = False,
-                    warmup_steps: int = 0, _prefix: str = "") -> nn.Module:
-    """Swaps every eligible ``nn.Linear`` for a ``TCFPLinear`` sharing the same
-    ``Parameter`` objects (tcfp/nn/__init__.py:1190-1351): names containing a
-    skip pattern are left alone, both dimensions must be multiples of 16 for
-    the tensor-core path, block scaling silently falls back to per-tensor for
-    layers whose dimensions the block size does not divide, and
-    ``_param_name`` becomes the dotted module path (the key of the
-    error-feedback state and of ``ef_state.pt``)."""
-    for name, child in list(model.named_children()):
-        full = f"{_prefix}.{name}" if _prefix else name
-        if any(p in name for p in skip_patterns):
+                    _parent_path: str = "") -> nn.Module:
+    """Swaps ``nn.Linear`` children for ``TCFPLinear`` in place, with the
+    signature, defaults and traversal of tcfp/nn/__init__.py:1190-1308:
+
+    * every child is recursed into FIRST; ``skip_patterns`` is matched against
+      the child's own name only, so a ``Linear`` inside a container called
+      ``head`` is still converted while a ``Linear`` named ``head`` is not;
+    * a ``Linear`` whose ``in_features`` the format block size does not divide
+      is left alone (:1276-1277);
+    * block scaling falls back to per-tensor scaling for layers whose
+      dimensions ``scale_block_size`` does not divide (:1285-1290);
+    * the new layer shares the old ``Parameter`` objects and ``_param_name``
+      is the dotted module path (the key of the error-feedback state and of
+      ``ef_state.pt``).
+
+    One difference, by scope: only the tensor-core path exists here.  Where
+    the reference would build a fake-quantize ``TCFPLinear`` -- when
+    ``use_tensor_cores`` is False (its default) or a dimension is not a
+    multiple of 16 (:1279-1282) -- the ``nn.Linear`` stays as it is.
+    ``nn.LayerNorm`` / ``nn.Embedding`` conversion (fake-quantize formats) is
+    likewise not provided.
+    """
+    for name, module in list(model.named_children()):
+        full_path = f"{_parent_path}.{name}" if _parent_path else name
+        convert_to_tcfp(module, mode, block_size, skip_patterns, nf4_residual=nf4_residual,
+                        nf_aware_scaling=nf_aware_scaling, stochastic_rounding=stochastic_rounding,
+                        warmup_steps=warmup_steps, use_tensor_cores=use_tensor_cores, hp_grad_weight=hp_grad_weight,
+                        error_feedback=error_feedback, delayed_scaling=delayed_scaling,
+                        use_fused_kernel=use_fused_kernel, use_cuda_ext=use_cuda_ext,
+                        scale_block_size=scale_block_size, abd=abd, srr=srr, _parent_path=full_path)
+        if any(pat in name for pat in skip_patterns):
             continue
-        if isinstance(child, nn.Linear) and not isinstance(child, TCFPLinear):
-            if child.in_features % 16 != 0 or child.out_features % 16 != 0:
-                continue
-            sbs = scale_block_size
-            if sbs is not None and (child.in_features % sbs != 0 or child.out_features % sbs != 0):
-                sbs = None
-            new = TCFPLinear(child.in_features, child.out_features, bias=child.bias is not None, mode=mode,
-                             block_size=block_size, warmup_steps=warmup_steps, use_tensor_cores=use_tensor_cores,
-                             hp_grad_weight=hp_grad_weight, error_feedback=error_feedback,
-                             delayed_scaling=delayed_scaling and sbs is None, scale_block_size=sbs, abd=abd, srr=srr,
-                             device=child.weight.device, dtype=child.weight.dtype)
-            new.weight = child.weight
-            if child.bias is not None:
-                new.bias = child.bias
-            new._param_name = full
-            setattr(model, name, new)
-        else:
-            convert_to_tcfp(child, mode, block_size, skip_patterns=skip_patterns, use_tensor_cores=use_tensor_cores,
-                            hp_grad_weight=hp_grad_weight, error_feedback=error_feedback,
-                            delayed_scaling=delayed_scaling, scale_block_size=scale_block_size, abd=abd, srr=srr,
-                            warmup_steps=warmup_steps, _prefix=full)
+        if not isinstance(module, nn.Linear) or isinstance(module, TCFPLinear):
+            continue
+        if module.in_features % block_size != 0:
+            continue
+        layer_tc = use_tensor_cores and module.in_features % 16 == 0 and module.out_features % 16 == 0
+        if not layer_tc:
+            continue
+        layer_sbs = scale_block_size
+        if layer_sbs is not None and (module.in_features % layer_sbs != 0 or module.out_features % layer_sbs != 0):
+            layer_sbs = None
+        new = TCFPLinear(module.in_features, module.out_features, bias=module.bias is not None, mode=mode,
+                         block_size=block_size, nf4_residual=nf4_residual, nf_aware_scaling=nf_aware_scaling,
+                         stochastic_rounding=stochastic_rounding, warmup_steps=warmup_steps, use_tensor_cores=True,
+                         hp_grad_weight=hp_grad_weight, error_feedback=error_feedback, delayed_scaling=delayed_scaling,
+                         use_fused_kernel=use_fused_kernel, use_cuda_ext=use_cuda_ext, scale_block_size=layer_sbs,
+                         abd=abd, srr=srr, device=module.weight.device, dtype=module.weight.dtype)
+        new._param_name = full_path
+        new.weight = module.weight
+        if module.bias is not None:
+            new.bias = module.bias
+        setattr(model, name, new)
     return model

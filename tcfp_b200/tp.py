@@ -11,6 +11,19 @@ their partial outputs with an all-reduce over NCCL (NVLink / NVSwitch).
 
 One process per GPU, ``torch.distributed`` for the plumbing.  The layer class
 is injectable so that the communication logic is testable on CPU with gloo.
+
+Overlap.  When the sharded layer is a ``TCFPLinear`` the collectives are
+started from inside its autograd Function (``nn.LayerHooks``): a row-parallel
+layer computes its output in row chunks and all-reduces chunk ``i`` on NCCL's
+stream while the GEMM of chunk ``i + 1`` runs; a column-parallel layer starts
+the all-reduce of its input gradient as soon as the dX GEMM is queued and
+computes the weight gradient underneath it.
+
+Scaling granularity.  With block scaling every shard's quantized bytes equal
+the unsharded layer's.  With per-tensor scaling each shard scales by its OWN
+amax (per-shard scaling, finer than the unsharded layer's single scale); the
+reference has no distributed form to match, and reproducing the unsharded
+scale would cost two dependent all-reduce(max) rounds per layer per step.
 """
 from __future__ import annotations
 
@@ -19,6 +32,32 @@ from typing import Callable
 import torch
 import torch.distributed as dist
 import torch.nn as nn
+
+
+_COLLECTIVES_ENABLED = True
+
+
+class collectives_disabled:
+    """Measurement aid: inside this context the data-path collectives of this
+    module return at once, leaving the local partial results in place.  The
+    numbers a model computes are then wrong; the time it takes is what the
+    step costs without communication, and the difference from the normal step
+    is the communication time that is not hidden behind compute."""
+
+    def __enter__(self):
+        global _COLLECTIVES_ENABLED
+        self._prev = _COLLECTIVES_ENABLED
+        _COLLECTIVES_ENABLED = False
+        return self
+
+    def __exit__(self, *exc):
+        global _COLLECTIVES_ENABLED
+        _COLLECTIVES_ENABLED = self._prev
+        return False
+
+
+def _active(group) -> bool:
+    return _COLLECTIVES_ENABLED and dist.is_initialized() and dist.get_world_size(group) > 1
 
 
 def shard_bounds(size: int, world: int, rank: int, granule: int = 1) -> tuple[int, int]:
@@ -48,8 +87,9 @@ class _CopyToParallel(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, g):
-        g = g.contiguous()
-        if dist.is_initialized() and dist.get_world_size(ctx.group) > 1:
+        if _active(ctx.group):
+            # reduce a private copy: autograd may hand the same gradient tensor to other consumers
+            g = g.clone(memory_format=torch.contiguous_format)
             dist.all_reduce(g, op=dist.ReduceOp.SUM, group=ctx.group)
         return g, None
 
@@ -59,9 +99,14 @@ class _ReduceFromParallel(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, group):
-        x = x.contiguous()
-        if dist.is_initialized() and dist.get_world_size(group) > 1:
-            dist.all_reduce(x, op=dist.ReduceOp.SUM, group=group)
+        if _active(group):
+            # the partial output is this rank's own fresh GEMM result: reduce it in place and tell autograd
+            if x.is_contiguous():
+                dist.all_reduce(x, op=dist.ReduceOp.SUM, group=group)
+                ctx.mark_dirty(x)
+            else:
+                x = x.contiguous()
+                dist.all_reduce(x, op=dist.ReduceOp.SUM, group=group)
         return x
 
     @staticmethod
@@ -78,6 +123,9 @@ class _ReduceFromParallel(torch.autograd.Function):
 def _all_gather_rows(x: torch.Tensor, group) -> torch.Tensor:
     world = dist.get_world_size(group)
     out = torch.empty((x.shape[0] * world,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+    if not _COLLECTIVES_ENABLED:           # measurement aid: right shape, local rows everywhere
+        out.view(world, *x.shape).copy_(x.unsqueeze(0).expand(world, *x.shape))
+        return out
     dist.all_gather_into_tensor(out, x.contiguous(), group=group)
     return out
 
@@ -85,7 +133,12 @@ def _all_gather_rows(x: torch.Tensor, group) -> torch.Tensor:
 def _reduce_scatter_rows(x: torch.Tensor, group) -> torch.Tensor:
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
+    if x.shape[0] % world != 0:
+        raise ValueError(f"sequence parallelism needs the token count ({x.shape[0]}) to be a multiple of the "
+                         f"tensor-parallel world size ({world})")
     rows = x.shape[0] // world
+    if not _COLLECTIVES_ENABLED:           # measurement aid: right shape, unreduced rows
+        return x[rank * rows:(rank + 1) * rows].clone()
     if x.is_cuda:
         out = torch.empty((rows,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
         dist.reduce_scatter_tensor(out, x.contiguous(), op=dist.ReduceOp.SUM, group=group)
@@ -146,27 +199,73 @@ def _default_factory(in_features: int, out_features: int, bias: bool, **kw) -> n
     return TCFPLinear(in_features, out_features, bias=bias, use_tensor_cores=True, **kw)
 
 
-class ColumnParallelLinear(nn.Module):
-    """``y_local = x @ W[rows of this rank].T``; output stays sharded."""
+def _is_tcfp(layer: nn.Module) -> bool:
+    from .nn import TCFPLinear
 
-    def __init__(self, in_features: int, out_features: int, bias: bool = True, *, group=None, granule: int = 16,
+    return isinstance(layer, TCFPLinear)
+
+
+class _Pending:
+    """Handle of an asynchronous collective; ``wait()`` makes the current
+    stream wait for it (no host synchronisation with NCCL)."""
+
+    def __init__(self, work):
+        self.work = work
+
+    def wait(self):
+        if self.work is not None:
+            self.work.wait()
+
+
+def _all_reduce_async(t: torch.Tensor, group):
+    if not _active(group):
+        return None
+    return _Pending(dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group, async_op=True))
+
+
+class ColumnParallelLinear(nn.Module):
+    """``y_local = x @ W[rows of this rank].T``; output stays sharded.
+
+    ``out_features`` may be a tuple: several projections fed by the same input
+    (q/k/v, gate/up) fused into ONE layer whose local weight is the
+    concatenation of this rank's shard of each part -- one weight quantizer
+    launch, one activation quantizer launch and one GEMM instead of one per
+    part, and a single input-gradient all-reduce.  ``forward`` then returns a
+    tuple of the parts' local outputs.  Scale blocks are per weight row, so
+    the fused layer's quantized bytes are those of the separate layers.
+    """
+
+    def __init__(self, in_features: int, out_features, bias: bool = True, *, group=None, granule: int = 16,
                  layer_factory: Callable[..., nn.Module] = _default_factory, reduce_input_grad: bool = True,
                  **layer_kw):
         super().__init__()
         self.group = group
-        # several column-parallel layers fed by one tensor (q/k/v, gate/up) share a single
-        # gradient all-reduce: the caller applies copy_to_parallel once and turns this off
+        # several column-parallel layers fed by one tensor may share a single gradient all-reduce:
+        # the caller applies copy_to_parallel once and turns this off
         self.reduce_input_grad = reduce_input_grad
         world = dist.get_world_size(group) if dist.is_initialized() else 1
         rank = dist.get_rank(group) if dist.is_initialized() else 0
-        self.out_start, self.out_end = shard_bounds(out_features, world, rank, granule)
+        self.fused = isinstance(out_features, (tuple, list))
+        parts = tuple(out_features) if self.fused else (out_features,)
+        self.bounds = [shard_bounds(n, world, rank, granule) for n in parts]
+        self.local_sizes = [e - s for s, e in self.bounds]
+        self.out_start, self.out_end = self.bounds[0]
         self.in_features, self.out_features = in_features, out_features
-        self.inner = layer_factory(in_features, self.out_end - self.out_start, bias, **layer_kw)
+        self.inner = layer_factory(in_features, sum(self.local_sizes), bias, **layer_kw)
+        # a TCFPLinear starts the gradient all-reduce itself, under its weight-gradient GEMM
+        self._overlap = reduce_input_grad and _is_tcfp(self.inner)
+        if self._overlap:
+            from .nn import LayerHooks
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        if self.reduce_input_grad:
+            self.inner._hooks = LayerHooks(dx_hook=lambda g: _all_reduce_async(g, self.group))
+
+    def forward(self, x: torch.Tensor):
+        if self.reduce_input_grad and not self._overlap:
             x = _CopyToParallel.apply(x, self.group)
-        return self.inner(x)
+        y = self.inner(x)
+        if self.fused:
+            return torch.split(y, self.local_sizes, dim=-1)
+        return y
 
 
 def copy_to_parallel(x: torch.Tensor, group=None) -> torch.Tensor:
@@ -175,11 +274,16 @@ def copy_to_parallel(x: torch.Tensor, group=None) -> torch.Tensor:
 
 
 class RowParallelLinear(nn.Module):
-    """``y = sum_ranks x[..., cols of this rank] @ W[:, cols].T`` (+ bias once)."""
+    """``y = sum_ranks x[..., cols of this rank] @ W[:, cols].T`` (+ bias once).
+
+    With a ``TCFPLinear`` inside, the partial output is produced in
+    ``overlap_chunks`` row chunks and each chunk's all-reduce runs while the
+    next chunk's GEMM does (the reduction happens in place, inside the layer's
+    autograd Function; the gradient of an all-reduced sum is the identity)."""
 
     def __init__(self, in_features: int, out_features: int, bias: bool = True, *, group=None, granule: int = 16,
                  layer_factory: Callable[..., nn.Module] = _default_factory, reduce_dtype: torch.dtype | None = None,
-                 sequence_parallel: bool = False, **layer_kw):
+                 sequence_parallel: bool = False, overlap_chunks: int = 4, **layer_kw):
         super().__init__()
         self.group = group
         # with sequence parallelism the output is reduce-scattered over tokens instead of all-reduced
@@ -192,15 +296,24 @@ class RowParallelLinear(nn.Module):
         self.inner = layer_factory(self.in_end - self.in_start, out_features, False, **layer_kw)
         # the bias is added after the reduction, once
         self.bias = nn.Parameter(torch.zeros(out_features)) if bias else None
+        inner_dtype = getattr(self.inner, "out_dtype", None)
+        self._overlap = (_is_tcfp(self.inner) and not sequence_parallel and world > 1
+                         and (reduce_dtype is None or reduce_dtype == inner_dtype))
+        if self._overlap:
+            from .nn import LayerHooks
+
+            self.inner._hooks = LayerHooks(out_hook=lambda y: _all_reduce_async(y, self.group),
+                                           row_chunks=overlap_chunks)
 
     def forward(self, x_shard: torch.Tensor) -> torch.Tensor:
         y = self.inner(x_shard)
-        if self.reduce_dtype is not None and y.dtype != self.reduce_dtype:
-            y = y.to(self.reduce_dtype)        # bf16 on the wire halves the NVLink bytes
-        if self.sequence_parallel:
-            y = _ScatterToSequenceParallel.apply(y, self.group)
-        else:
-            y = _ReduceFromParallel.apply(y, self.group)
+        if not self._overlap:
+            if self.reduce_dtype is not None and y.dtype != self.reduce_dtype:
+                y = y.to(self.reduce_dtype)        # bf16 on the wire halves the NVLink bytes
+            if self.sequence_parallel:
+                y = _ScatterToSequenceParallel.apply(y, self.group)
+            else:
+                y = _ReduceFromParallel.apply(y, self.group)
         if self.bias is not None:
             # under sequence parallelism every rank adds the bias to its own tokens only, so the
             # bias gradient is a partial sum: all-reduce it on the way back

@@ -10,7 +10,7 @@ import torch.distributed as dist
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .tp import ColumnParallelLinear, ParallelMLP, RowParallelLinear, copy_to_parallel
+from .tp import ColumnParallelLinear, ParallelMLP, RowParallelLinear, gather_from_sequence_parallel
 
 
 def _world() -> int:
@@ -28,47 +28,87 @@ class RMSNorm(nn.Module):
 
 
 class DecoderLayer(nn.Module):
-    """Pre-norm Llama-style block, tensor-parallel: q/k/v/gate/up column-parallel
-    (heads and FFN columns split on scale-block boundaries), o/down row-parallel
-    with a bf16 all-reduce of the partial outputs."""
+    """Pre-norm Llama-style block, tensor-parallel: q/k/v and gate/up are fused
+    column-parallel layers (heads and FFN columns split on scale-block
+    boundaries; one quantize + one GEMM per group), o/down row-parallel with a
+    bf16 reduction of the partial outputs.
 
-    def __init__(self, d_model: int, n_heads: int, ffn: int, *, granule: int = 64, **layer_kw):
+    ``sequence_parallel=False``: activations between the blocks are replicated,
+    row-parallel outputs are all-reduced (chunked under the GEMM), the input
+    gradients of the column-parallel groups are all-reduced under their
+    weight-gradient GEMMs.  ``sequence_parallel=True``: activations between the
+    blocks are sharded over tokens -- norms and residual adds touch tokens /
+    world rows -- with an all-gather before each column-parallel group and a
+    reduce-scatter after each row-parallel layer (same bytes on the wire)."""
+
+    def __init__(self, d_model: int, n_heads: int, ffn: int, *, granule: int = 64, sequence_parallel: bool = False,
+                 overlap_chunks: int = 4, **layer_kw):
         super().__init__()
         world = _world()
         assert n_heads % world == 0, "heads must divide over the tensor-parallel ranks"
+        self.sp = sequence_parallel and world > 1
         self.head_dim = d_model // n_heads
         self.heads_local = n_heads // world
-        col = dict(bias=False, granule=max(granule, self.head_dim), reduce_input_grad=False, **layer_kw)
+        g_attn = max(granule, self.head_dim)
         self.norm1 = RMSNorm(d_model)
-        self.q = ColumnParallelLinear(d_model, d_model, **col)
-        self.k = ColumnParallelLinear(d_model, d_model, **col)
-        self.v = ColumnParallelLinear(d_model, d_model, **col)
-        self.o = RowParallelLinear(d_model, d_model, bias=False, granule=max(granule, self.head_dim),
-                                   reduce_dtype=torch.bfloat16, **layer_kw)
+        self.qkv = ColumnParallelLinear(d_model, (d_model, d_model, d_model), bias=False, granule=g_attn,
+                                        reduce_input_grad=not self.sp, **layer_kw)
+        self.o = RowParallelLinear(d_model, d_model, bias=False, granule=g_attn, reduce_dtype=torch.bfloat16,
+                                   sequence_parallel=self.sp, overlap_chunks=overlap_chunks, **layer_kw)
         self.norm2 = RMSNorm(d_model)
-        colf = dict(bias=False, granule=granule, reduce_input_grad=False, **layer_kw)
-        self.gate = ColumnParallelLinear(d_model, ffn, **colf)
-        self.up = ColumnParallelLinear(d_model, ffn, **colf)
-        self.down = RowParallelLinear(ffn, d_model, bias=False, granule=granule, reduce_dtype=torch.bfloat16, **layer_kw)
+        self.gate_up = ColumnParallelLinear(d_model, (ffn, ffn), bias=False, granule=granule,
+                                            reduce_input_grad=not self.sp, **layer_kw)
+        self.down = RowParallelLinear(ffn, d_model, bias=False, granule=granule, reduce_dtype=torch.bfloat16,
+                                      sequence_parallel=self.sp, overlap_chunks=overlap_chunks, **layer_kw)
 
-    def forward(self, x):                      # x: (B, T, d) bf16
-        B, T, _ = x.shape
-        h = copy_to_parallel(self.norm1(x))
+    def forward(self, x):                      # x: (B, T, d) bf16; with sequence parallelism (B*T/world, d)
+        B, T = self.batch_shape if self.sp else x.shape[:2]
+        h = self.norm1(x)
+        if self.sp:
+            h = gather_from_sequence_parallel(h)
+        q, k, v = self.qkv(h)
         shp = (B, T, self.heads_local, self.head_dim)
-        q = self.q(h).view(shp).transpose(1, 2)
-        k = self.k(h).view(shp).transpose(1, 2)
-        v = self.v(h).view(shp).transpose(1, 2)
-        a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
-        a = a.transpose(1, 2).reshape(B, T, self.heads_local * self.head_dim)
+        a = F.scaled_dot_product_attention(q.reshape(shp).transpose(1, 2), k.reshape(shp).transpose(1, 2),
+                                           v.reshape(shp).transpose(1, 2), is_causal=True)
+        a = a.transpose(1, 2).reshape(q.shape[:-1] + (self.heads_local * self.head_dim,))
         x = x + self.o(a)
-        h = copy_to_parallel(self.norm2(x))
-        f = F.silu(self.gate(h)) * self.up(h)
-        return x + self.down(f)
+        h = self.norm2(x)
+        if self.sp:
+            h = gather_from_sequence_parallel(h)
+        gate, up = self.gate_up(h)
+        return x + self.down(F.silu(gate) * up)
 
 
-def build_decoder(n_layers=4, d_model=4096, n_heads=32, ffn=11008, block=64, **layer_kw) -> nn.Module:
+class Decoder(nn.Module):
+    """A stack of decoder blocks.  Input and output are ``(B, T, d)``; under
+    sequence parallelism the stack works on this rank's token shard in between."""
+
+    def __init__(self, layers: list[DecoderLayer]):
+        super().__init__()
+        self.layers = nn.ModuleList(layers)
+        self.sp = bool(layers) and layers[0].sp
+
+    def forward(self, x):
+        if not self.sp:
+            for layer in self.layers:
+                x = layer(x)
+            return x
+        B, T, d = x.shape
+        world, rank = dist.get_world_size(), dist.get_rank()
+        tokens = x.reshape(B * T, d)
+        rows = tokens.shape[0] // world
+        h = tokens[rank * rows:(rank + 1) * rows]
+        for layer in self.layers:
+            layer.batch_shape = (B, T)
+            h = layer(h)
+        return gather_from_sequence_parallel(h).reshape(B, T, d)
+
+
+def build_decoder(n_layers=4, d_model=4096, n_heads=32, ffn=11008, block=64, *, sequence_parallel=False,
+                  overlap_chunks=4, **layer_kw) -> nn.Module:
     kw = dict(scale_block_size=block, out_dtype=torch.bfloat16, **layer_kw)
-    m = nn.Sequential(*[DecoderLayer(d_model, n_heads, ffn, granule=block, **kw) for _ in range(n_layers)])
+    m = Decoder([DecoderLayer(d_model, n_heads, ffn, granule=block, sequence_parallel=sequence_parallel,
+                              overlap_chunks=overlap_chunks, **kw) for _ in range(n_layers)])
     _name_layers(m)
     _init_weights(m)
     return m

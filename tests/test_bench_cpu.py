@@ -6,6 +6,8 @@ import sys
 from pathlib import Path
 
 ROOT = Path(__file__).resolve().parent.parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
 
 
 def test_reference_arm_prints_contract_line():
@@ -19,3 +21,17 @@ def test_reference_arm_prints_contract_line():
     assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["d2h_bytes_per_step"] == 0
     assert line["e2e"]["value"] == line["value"]
     assert "workload" in line["config"]
+    # whole passes, reported as run: no extrapolation from a slice, no echoed step count
+    assert line["steps"] == 1 and line["warmup"] == 0 and "whole pass" in line["cpu_baseline"]["sample"]
+    assert line["ms_per_step"] > 0 and abs(line["value"] - 4 * 8192**3 / (line["ms_per_step"] * 1e-3) / 1e12) < 1e-6 * line["value"] + 1e-9
+    # both arms describe the workload with the same config keys
+    import bench
+
+    assert set(line["config"]) == set(bench._config(1))
+
+
+def test_roofline_traffic_is_read_from_the_kept_profile():
+    import bench
+
+    traffic, src = bench._profiled_traffic()
+    assert src == "profiles/dual_gemm_pair_mxf8_8192_bench.md" and 4.48e8 < traffic < 2e9

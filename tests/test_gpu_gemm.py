@@ -204,3 +204,57 @@ def test_bounded_wait_gives_up_and_reports(lib):
     out = fused_dual_gemm_forward(d(a), d(hi), d(lo), d(ia), d(ihi), d(ilo))
     assert rel_fro(out, O.dual_gemm_nt(a, ia, hi, ihi, lo, ilo)) <= TOL
     assert lib.tcfp_selftest_bounded_wait(0, None) == -1
+
+
+@pytest.mark.parametrize("bs", [32, 64, 128])
+def test_block_retarget_is_exact_up_to_e4m3_underflow(bs):
+    """The weight re-targeted for the dX contraction dequantizes to the same
+    values as the quantized weight it came from: bit-equal wherever the
+    exponent shift keeps the value on E4M3's grid, and within 2^-10 * 2^t of
+    it where the shift runs into the subnormal step."""
+    from tcfp_b200.kernels import block_retarget
+
+    D_out, D_in = 384, 640
+    w = weights(410, D_out, D_in, outliers=True)
+    w[5] = 0.0                                      # zero rows: -128 sentinel in the residual plane
+    w[:, 64:96] *= 1e-3                             # a column block of small rows next to large ones
+    hi, lo, eh, el, _ = O.dual_quantize_block(w, bs)
+    d = lambda t: t.to(DEV)  # noqa: E731
+    hi_t, lo_t, t_hi, t_lo = block_retarget(d(hi), d(lo), d(eh), d(el), bs)
+    assert hi_t.shape == (D_in, D_out) and t_hi.shape == (D_out // bs, D_in)
+    for codes, exps, codes_t, t, sentinel in ((hi, eh, hi_t, t_hi, False), (lo, el, lo_t, t_lo, True)):
+        ref = (O._deq_lo(codes, exps, bs) if sentinel else O.block_dequantize(codes, exps, bs)).double()   # (D_out, D_in)
+        scale_t = torch.exp2(t.cpu().double()).repeat_interleave(bs, dim=0)                 # (D_out, D_in)
+        got = codes_t.cpu().float().double().t() * scale_t
+        bound = 2.0 ** -10 * scale_t
+        assert bool(((got - ref).abs() <= bound).all())
+        exact = (got == ref).double().mean().item()
+        assert exact > 0.93, f"only {exact:.3f} of the values survived the re-encoding bit for bit"
+        # t is the largest live exponent of each (row block, column) -- nothing overflows
+        assert int(codes_t.view(torch.uint8).cpu().bitwise_and(0x7F).max()) <= 0x7E
+    # residual left out (asymmetric backward)
+    hi_t2, lo_t2, t_hi2, t_lo2 = block_retarget(d(hi), None, d(eh), None, bs)
+    assert lo_t2 is None and t_lo2 is None and torch.equal(hi_t2.view(torch.uint8), hi_t.view(torch.uint8))
+
+
+@pytest.mark.parametrize("bs", [32, 128])
+def test_block_backward_dx_routes_agree_and_reuse_the_retargeted_weight(bs):
+    from tcfp_b200.kernels import fused_block_scaled_backward_dx
+
+    M, D_out, D_in = 512, 256, 384
+    g = acts(420, M, D_out, torch.float32)
+    w = weights(421, D_out, D_in, outliers=True)
+    gq, eg = O.block_quantize(g, bs, torch.float8_e5m2)
+    hi, lo, eh, el, _ = O.dual_quantize_block(w, bs)
+    ref = O.block_backward_dx(gq, eg, hi, eh, lo, el, bs)
+    d = lambda t: t.to(DEV)  # noqa: E731
+    dhi, dlo, deh, del_ = d(hi), d(lo), d(eh), d(el)
+    fp8 = fused_block_scaled_backward_dx(d(gq), dhi, dlo, d(eg), deh, del_, bs)
+    cached = dhi._tcfp_dx
+    again = fused_block_scaled_backward_dx(d(gq), dhi, dlo, d(eg), deh, del_, bs)
+    assert dhi._tcfp_dx is cached and torch.equal(again, fp8)
+    exact = fused_block_scaled_backward_dx(d(gq), dhi, dlo, d(eg), deh, del_, bs, exact_bf16=True)
+    assert rel_fro(fp8, ref) <= TOL and rel_fro(exact, ref) <= TOL and rel_fro(fp8, exact) <= 1e-4
+    hi_only = fused_block_scaled_backward_dx(d(gq), dhi, None, d(eg), deh, None, bs, out_dtype=torch.bfloat16)
+    assert hi_only.dtype == torch.bfloat16
+    assert rel_fro(hi_only.float(), O.block_backward_dx(gq, eg, hi, eh, None, None, bs)) <= 5e-3

@@ -157,7 +157,7 @@ def test_convert_and_mlp_training_step_loss_decreases():
 
     torch.manual_seed(0)
     model = torch.nn.Sequential(torch.nn.Linear(64, 256), torch.nn.GELU(), torch.nn.Linear(256, 64)).to(DEV)
-    convert_to_tcfp(model, skip_patterns=())
+    convert_to_tcfp(model, skip_patterns=(), use_tensor_cores=True)
     assert isinstance(model[0], TCFPLinear) and model[0]._param_name == "0" and model[2]._param_name == "2"
     x = torch.randn(128, 64, device=DEV)
     target = torch.randn(128, 64, device=DEV)
@@ -360,3 +360,61 @@ def test_error_feedback_reduces_accumulated_error():
     e_ef = float((acc_ef / n - w).norm())
     e_no = float((acc_no / n - w).norm())
     assert err.abs().max() > 0 and e_ef < 0.5 * e_no
+
+
+@pytest.mark.parametrize("kw", [dict(scale_block_size=64), dict(), dict(scale_block_size=32, error_feedback=False)],
+                         ids=["block64_ef", "per_tensor_ef", "block32_no_ef"])
+def test_quantized_weight_is_reused_between_optimizer_steps(kw):
+    """Gradient-accumulation micro-batches and recomputation re-run the
+    forward on an unchanged weight: the quantized weight is computed once and
+    reused, the outputs are bit-identical to a layer that re-quantizes on
+    every forward, the error buffer is untouched, and an optimizer step (or any
+    in-place weight edit) invalidates the reuse."""
+    from tcfp_b200 import kernels as K
+    from tcfp_b200 import nn as tnn
+    from tcfp_b200.nn import TCFPLinear
+
+    torch.manual_seed(5)
+    cached = TCFPLinear(256, 384, use_tensor_cores=True, **kw).to(DEV)
+    plain = TCFPLinear(256, 384, use_tensor_cores=True, **kw).to(DEV)
+    plain.load_state_dict(cached.state_dict())
+    cached._param_name = plain._param_name = "w"
+    xs = [acts(80 + i, 128, 256).to(DEV) for i in range(3)]
+    calls = {"n": 0}
+    orig_block, orig_pt = tnn.fused_dual_quantize_fp8, tnn.dual_quantize_per_tensor
+
+    def counting(fn):
+        def wrapped(*a, **k):
+            calls["n"] += 1
+            return fn(*a, **k)
+        return wrapped
+
+    tnn.fused_dual_quantize_fp8, tnn.dual_quantize_per_tensor = counting(orig_block), counting(orig_pt)
+    try:
+        outs = []
+        for x in xs:                                   # three micro-batches, no optimizer step in between
+            y = cached(x)
+            y.square().mean().backward()
+            outs.append(y.detach())
+        has_ef = cached._error_state is not None
+        # EF: one updating quantization + one read-only quantization shared by micro-batches 2 and 3
+        assert calls["n"] == (2 if has_ef else 1)
+        ef_after = cached._error_state._buffers["w"].clone() if has_ef else None
+        with torch.no_grad():
+            again = cached(xs[2])                      # recomputation: still the same quantized weight
+        assert calls["n"] == (2 if has_ef else 1) and torch.equal(again, outs[2])
+    finally:
+        tnn.fused_dual_quantize_fp8, tnn.dual_quantize_per_tensor = orig_block, orig_pt
+    for x, y in zip(xs, outs):
+        plain._wq_cache.clear()                        # never a hit: re-quantizes on every forward
+        assert torch.equal(plain(x).detach(), y)
+        plain._wq_cache.clear()
+    if has_ef:
+        assert torch.equal(cached._error_state._buffers["w"], ef_after)
+        assert torch.equal(plain._error_state._buffers["w"], ef_after)
+    # an in-place weight edit invalidates the reuse
+    with torch.no_grad():
+        cached.weight.mul_(1.5)
+        plain.weight.mul_(1.5)
+    assert torch.equal(cached(xs[0]).detach(), plain(xs[0]).detach())
+    assert K.is_triton_available()

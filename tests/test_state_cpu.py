@@ -55,7 +55,7 @@ def test_error_buffer_is_lazy_fp32_and_rebinds():
 
 def test_ef_state_schema_round_trip(tmp_path):
     model = torch.nn.Sequential(torch.nn.Linear(32, 64), torch.nn.ReLU(), torch.nn.Linear(64, 32))
-    convert_to_tcfp(model, skip_patterns=(), delayed_scaling=True)
+    convert_to_tcfp(model, skip_patterns=(), use_tensor_cores=True, delayed_scaling=True)
     l0 = model[0]
     assert isinstance(l0, TCFPLinear) and l0._param_name == "0"
     st = l0._error_state
@@ -68,7 +68,7 @@ def test_ef_state_schema_round_trip(tmp_path):
     assert set(snap["0"]) == {"_buffers", "_amax_ema", "_delayed_amax", "_residual_ratio", "_step_count", "_ema_decay"}
     save_ef_state(model, tmp_path / "ef_state.pt")
     fresh = torch.nn.Sequential(torch.nn.Linear(32, 64), torch.nn.ReLU(), torch.nn.Linear(64, 32))
-    convert_to_tcfp(fresh, skip_patterns=(), delayed_scaling=True)
+    convert_to_tcfp(fresh, skip_patterns=(), use_tensor_cores=True, delayed_scaling=True)
     load_ef_state(fresh, tmp_path / "ef_state.pt")
     f = fresh[0]._error_state
     assert torch.equal(f._buffers["0"], st._buffers["0"]) and f._step_count["0.steps"] == 7
@@ -140,3 +140,84 @@ def test_state_machine_is_bit_identical_to_the_reference_class():
         d1, d2 = getattr(r, table), getattr(o, table)
         assert d1.keys() == d2.keys() and all(torch.equal(d1[k], d2[k]) for k in d1)
     assert r._step_count == o._step_count
+
+
+def _nested_model():
+    nn = torch.nn
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.proj = nn.Linear(64, 128)
+            self.odd = nn.Linear(48, 64)            # 48 % 32 != 0 -> format block size skip
+            self.tiny = nn.Linear(64, 24)           # out_features % 16 != 0 -> no tensor-core layer
+            self.head = nn.Linear(64, 64)           # own name matches the skip pattern
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.blocks = nn.ModuleList([Block(), Block()])
+            self.head = nn.Sequential(nn.Linear(128, 64), nn.ReLU(), nn.Linear(64, 128, bias=False))
+            self.out_head = nn.Linear(64, 64)
+            self.narrow = nn.Linear(96, 64)          # 96 % 64 != 0 -> per-tensor fallback of block scaling
+
+    return Net()
+
+
+def test_convert_to_tcfp_signature_and_traversal_match_the_reference():
+    """Same positional order, defaults and converted-module set as
+    tcfp/nn/__init__.py:1190-1308, checked against the reference function
+    itself when ``oracle/_ref`` holds it (differential), and against the
+    written-down expectation otherwise."""
+    import inspect
+    import warnings
+
+    from oracle import ref_loader
+
+    sig = inspect.signature(convert_to_tcfp)
+    names = list(sig.parameters)
+    assert names[:4] == ["model", "mode", "block_size", "skip_patterns"]
+    assert sig.parameters["skip_patterns"].kind is inspect.Parameter.POSITIONAL_OR_KEYWORD
+    assert sig.parameters["use_tensor_cores"].default is False
+    for kw in ("nf4_residual", "nf_aware_scaling", "stochastic_rounding", "use_fused_kernel", "use_cuda_ext",
+               "_parent_path"):
+        assert sig.parameters[kw].kind is inspect.Parameter.KEYWORD_ONLY
+
+    from tcfp_b200.core import TCFPMode
+
+    ours = _nested_model()
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        convert_to_tcfp(ours, TCFPMode.TCFP12, 32, ("head",), use_tensor_cores=True, scale_block_size=64,
+                        use_fused_kernel=True, use_cuda_ext=True, nf4_residual=False)
+    mine = {n: (m.scale_block_size, m._param_name) for n, m in ours.named_modules() if isinstance(m, TCFPLinear)}
+    # a Linear inside the container called "head" IS converted; Linears named "...head" are not
+    assert set(mine) == {"blocks.0.proj", "blocks.1.proj", "head.0", "head.2", "narrow"}
+    assert all(v[1] == k for k, v in mine.items())
+    assert mine["narrow"][0] is None and mine["head.0"][0] == 64
+    assert ours.head[2].bias is None and isinstance(ours.blocks[0].odd, torch.nn.Linear)
+
+    # default call converts nothing here (use_tensor_cores defaults to False: fake-quantize is not provided)
+    plain = _nested_model()
+    convert_to_tcfp(plain)
+    assert not any(isinstance(m, TCFPLinear) for m in plain.modules())
+
+    if not ref_loader.available():
+        return
+    ref = ref_loader.load_reference()
+    try:
+        theirs = _nested_model()
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            ref.nn.convert_to_tcfp(theirs, ref.core.TCFPMode.TCFP12, 32, ("head",), use_tensor_cores=True,
+                                   scale_block_size=64)
+        got = {n: (m.scale_block_size, m._param_name) for n, m in theirs.named_modules()
+               if isinstance(m, ref.nn.TCFPLinear) and m.use_tensor_cores}
+        assert got == mine
+        ref_sig = inspect.signature(ref.nn.convert_to_tcfp)
+        assert list(ref_sig.parameters) == names
+        for n in names[1:]:
+            assert ref_sig.parameters[n].default == sig.parameters[n].default or n == "mode"
+            assert ref_sig.parameters[n].kind == sig.parameters[n].kind
+    finally:
+        ref_loader.unload()

@@ -78,6 +78,12 @@ def _worker(rank: int, world: int, port: int, ret):
         ok &= torch.allclose(sp.up.inner.weight.grad, ref_up.weight.grad[s:e], atol=1e-5)
         ok &= torch.allclose(sp.down.inner.weight.grad, ref_down.weight.grad[:, s:e], atol=1e-5)
         ok &= torch.allclose(sp.down.bias.grad, ref_down.bias.grad, atol=1e-5)
+        # a token count the world size does not divide is refused, not truncated
+        try:
+            sp.down(torch.randn(3, e - s))
+            ok = False
+        except ValueError as e:
+            ok &= "multiple of the tensor-parallel world size" in str(e)
         ret[rank] = bool(ok)
     finally:
         dist.destroy_process_group()
