@@ -140,6 +140,23 @@ int32_t tcfp_quantize(const void* x, int32_t x_dtype, uint8_t* out,
 
 /* bytes of the packed E8M0 scale-factor array for a (rows, K) operand */
 size_t tcfp_sf_packed_bytes(int64_t rows, int64_t K, int32_t block_size);
+/*
+ * tcfp_quantize of a gradient that ALSO returns its column sums -- the bias
+ * gradient, which the reference takes with a separate full pass over the
+ * gradient (grad_2d.sum(dim=0), tcfp/nn/__init__.py:558, 753).  block_size 0:
+ * one pass yields the amax and the sums, the cast follows (tcfp/core.py:
+ * 137-158); block_size 32/64/128: the block quantizer accumulates the sums as
+ * it goes (tcfp/kernels.py:205-275).  colsum_out: C floats.  The summation
+ * order is fixed (per 256-row group, then the groups in order), so repeated
+ * calls return identical bits.  workspace: tcfp_colsum_workspace_bytes(R, C)
+ * bytes of device memory, 16-byte aligned.
+ */
+size_t tcfp_colsum_workspace_bytes(int64_t R, int64_t C);
+int32_t tcfp_quantize_colsum(const void* x, int32_t x_dtype, uint8_t* out,
+                             void* scale_out, uint8_t* sf_out, int64_t R,
+                             int64_t C, int32_t block_size, int32_t fmt,
+                             float* colsum_out, void* workspace, void* stream);
+
 /* int8 exponent plane (K/bs, rows) -> packed E8M0 chunks (for callers that
  * hold only the reference-layout planes) */
 int32_t tcfp_pack_scales(const int8_t* exps, uint8_t* sf_out, int64_t rows,

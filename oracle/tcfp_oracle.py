@@ -39,8 +39,9 @@ _PHILOX_ROUND_A = np.uint64(0xD2511F53)
 _PHILOX_ROUND_B = np.uint64(0xCD9E8D57)
 
 
-def philox4x32_10(seed: int, counter: np.ndarray) -> np.ndarray:
-    """First 32-bit output word of Philox4x32-10.
+def philox4x32_10(seed: int, counter: np.ndarray, all_words: bool = False) -> np.ndarray:
+    """First 32-bit output word of Philox4x32-10 (all four, stacked on axis 0,
+    with ``all_words``).
 
     key = (seed & 2^32-1, seed >> 32); counter words = (ctr & 2^32-1,
     ctr >> 32, 0, 0).  This is the published Philox algorithm (Salmon et al.,
@@ -65,7 +66,15 @@ def philox4x32_10(seed: int, counter: np.ndarray) -> np.ndarray:
             c0, c1, c2, c3 = n0, n1, n2, n3
             k0 = np.uint32((int(k0) + int(_PHILOX_KEY_A)) & 0xFFFFFFFF)
             k1 = np.uint32((int(k1) + int(_PHILOX_KEY_B)) & 0xFFFFFFFF)
+    if all_words:
+        return np.stack([c0, c1, c2, c3])
     return c0
+
+
+def _word_to_uniform(w: np.ndarray) -> np.ndarray:
+    w = w.view(np.int32).astype(np.int64)
+    w = np.where(w < 0, -w - 1, w)
+    return w.astype(np.float32) * np.float32(4.6566127342e-10)
 
 
 def philox_uniform(seed: int, offset: int, numel: int) -> torch.Tensor:
@@ -79,10 +88,23 @@ def philox_uniform(seed: int, offset: int, numel: int) -> torch.Tensor:
     ``n*K + k`` (tcfp/kernels.py:415-417).
     """
     idx = np.arange(numel, dtype=np.uint64) + np.uint64(offset)
-    w = philox4x32_10(seed, idx).view(np.int32).astype(np.int64)
-    w = np.where(w < 0, -w - 1, w)
-    u = w.astype(np.float32) * np.float32(4.6566127342e-10)
-    return torch.from_numpy(u)
+    return torch.from_numpy(_word_to_uniform(philox4x32_10(seed, idx)))
+
+
+def philox_uniform_packed(seed: int, offset: int, numel: int) -> torch.Tensor:
+    """Uniforms of the PER-TENSOR stochastic paths, whose stream is this
+    build's own definition (the reference draws ``torch.rand_like`` there,
+    tcfp/core.py:462, which no other implementation can reproduce): element
+    ``j = offset + i`` takes output word ``j & 3`` of
+    ``philox4x32_10(seed, j >> 2)`` -- all four words of every generator call
+    are used -- through the same word -> float mapping as above."""
+    idx = np.arange(numel, dtype=np.uint64) + np.uint64(offset)
+    first = int(offset) >> 2
+    last = (int(offset) + max(numel, 1) - 1) >> 2
+    words = philox4x32_10(seed, np.arange(first, last + 1, dtype=np.uint64), all_words=True)   # (4, calls)
+    call = (idx >> np.uint64(2)).astype(np.int64) - first
+    lane = (idx & np.uint64(3)).astype(np.int64)
+    return torch.from_numpy(_word_to_uniform(np.ascontiguousarray(words[lane, call])))
 
 
 # ---------------------------------------------------------------------------
@@ -176,7 +198,7 @@ def dual_quantize_per_tensor(
     cur_lo = residual.abs().max()
     s_lo = (FP8_E4M3_MAX / (cur_lo.clamp(min=1e-12) if amax_lo is None else amax_lo)).to(torch.float32)
     if srr:
-        rand = philox_uniform(seed, offset, w.numel()).reshape(w.shape)
+        rand = philox_uniform_packed(seed, offset, w.numel()).reshape(w.shape)
         w_lo, inv_lo = to_fp8_e4m3_sr(residual, rand, scale=s_lo)
     else:
         w_lo, inv_lo = to_fp8_e4m3(residual, scale=s_lo)
@@ -413,7 +435,7 @@ def linear_forward(x, weight, bias, state: LayerState | None, *, srr=False, abd=
         residual = w - w_hi.float() * inv_hi
         if srr:
             off = state.srr_offset if state is not None else 0
-            rand = philox_uniform(seed, off, w.numel()).reshape(w.shape)
+            rand = philox_uniform_packed(seed, off, w.numel()).reshape(w.shape)
             if state is not None:
                 state.srr_offset += w.numel()
             w_lo, inv_lo = to_fp8_e4m3_sr(residual, rand)

@@ -32,6 +32,9 @@ _SIGNATURES = {
     "tcfp_quantize": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                 c_int32, c_int32, c_void_p, c_void_p, c_int32, c_uint64, c_uint64, c_void_p,
                                 c_void_p]),
+    "tcfp_colsum_workspace_bytes": (c_size_t, [c_int64, c_int64]),
+    "tcfp_quantize_colsum": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int32,
+                                       c_int32, c_void_p, c_void_p, c_void_p]),
     "tcfp_sf_packed_bytes": (c_size_t, [c_int64, c_int64, c_int32]),
     "tcfp_pack_scales": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_int32, c_void_p]),
     "tcfp_block_dequantize_bf16": (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int32, c_int32,

@@ -67,6 +67,24 @@ def to_fp8_e5m2(tensor: torch.Tensor, scale: torch.Tensor | None = None):
     return _cast(tensor, scale, torch.float8_e5m2, _C.E5M2, "to_fp8_e5m2")
 
 
+def to_fp8_e5m2_with_colsum(grad2d: torch.Tensor):
+    """``to_fp8_e5m2`` of a 2-D gradient plus its FP32 column sums (the bias
+    gradient, tcfp/nn/__init__.py:558): the pass that finds the amax also
+    accumulates the sums, instead of a separate ``sum(dim=0)`` read.  Returns
+    ``(fp8, inv_scale (1,), colsum (C,))``."""
+    _require_cuda(grad2d, "to_fp8_e5m2_with_colsum")
+    assert grad2d.ndim == 2 and grad2d.is_contiguous() and grad2d.dtype in (torch.float32, torch.bfloat16)
+    R, C = grad2d.shape
+    lib = _C.load()
+    out = torch.empty((R, C), device=grad2d.device, dtype=torch.float8_e5m2)
+    inv = torch.empty(1, device=grad2d.device, dtype=torch.float32)
+    colsum = torch.empty(C, device=grad2d.device, dtype=torch.float32)
+    ws = torch.empty(lib.tcfp_colsum_workspace_bytes(R, C), dtype=torch.uint8, device=grad2d.device)
+    _C.check(lib.tcfp_quantize_colsum(_C.ptr(grad2d), _C.dtype_code(grad2d), _C.ptr(out), _C.ptr(inv), None, R, C, 0,
+                                      _C.E5M2, _C.ptr(colsum), _C.ptr(ws), _C.stream()))
+    return out, inv, colsum
+
+
 def nf_aware_target_max(tensor: torch.Tensor, sigma_factor: float = 3.0) -> torch.Tensor:
     """The effective maximum of tcfp/core.py:182-185: ``sigma_factor * std``,
     or the amax for near-constant tensors (std < 1e-6).  The standard
@@ -136,7 +154,8 @@ def dual_quantize_per_tensor(weight: torch.Tensor, error: torch.Tensor | None = 
 
 def to_fp8_e4m3_sr(tensor: torch.Tensor, scale: torch.Tensor | None = None, *, seed: int = 0, offset: int = 0):
     """tcfp/core.py:109-134 with a seeded Philox stream in place of
-    ``torch.rand_like``: element ``i`` draws ``philox4x32-10(seed, offset + i)``."""
+    ``torch.rand_like``: element ``i`` draws word ``(offset + i) & 3`` of
+    ``philox4x32-10(seed, (offset + i) >> 2)`` (all four words of a call are used)."""
     return _cast(tensor, scale, torch.float8_e4m3fn, _C.E4M3, "to_fp8_e4m3_sr", stochastic=True, seed=seed,
                  offset=offset)
 

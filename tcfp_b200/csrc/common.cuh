@@ -51,6 +51,14 @@ __device__ __forceinline__ float decode_fp8_fast(uint32_t c) {
   return __uint_as_float(__float_as_uint(v) | ((c & 0x80u) << 24));
 }
 
+// two codes (low 16 bits of c) -> two floats through the hardware converter:
+// fp8x2 -> f16x2 is exact, f16 -> f32 is exact
+template <bool E5M2>
+__device__ __forceinline__ float2 decode_fp8x2(uint32_t c) {
+  const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(c & 0xFFFFu), E5M2 ? __NV_E5M2 : __NV_E4M3);
+  return __half22float2(__half2(h));
+}
+
 __device__ __forceinline__ float clampf(float x, float lim) {
   return fminf(fmaxf(x, -lim), lim);
 }
@@ -106,17 +114,16 @@ __device__ __forceinline__ float exp2_int(int e) {
 }
 
 // ---- Philox4x32-10 ---------------------------------------------------------
-// u = f(first word of philox4x32-10(key = seed, counter = (ctr_lo, ctr_hi, 0, 0)))
-// f: reinterpret as int32, x<0 -> -x-1, times 4.6566127342e-10f.
-// This is the stream tl.rand(seed, offset) produces, which the reference's
-// block quantizer draws at offset n*K + k (tcfp/kernels.py:415-417).
-__device__ __forceinline__ float philox_uniform(uint64_t seed, uint64_t ctr) {
+// The four output words of philox4x32-10(key = seed, counter = (ctr_lo, ctr_hi, 0, 0)).
+// High and low halves of the round products as separate 32-bit multiplies:
+// measured faster on sm_100 than forming the 64-bit products.
+__device__ __forceinline__ uint4 philox4x32_10(uint64_t seed, uint64_t ctr) {
   uint32_t c0 = (uint32_t)ctr, c1 = (uint32_t)(ctr >> 32), c2 = 0u, c3 = 0u;
   uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
 #pragma unroll
   for (int r = 0; r < 10; ++r) {
-    uint32_t hb = __umulhi(0xCD9E8D57u, c2), lb = 0xCD9E8D57u * c2;
-    uint32_t ha = __umulhi(0xD2511F53u, c0), la = 0xD2511F53u * c0;
+    const uint32_t hb = __umulhi(0xCD9E8D57u, c2), lb = 0xCD9E8D57u * c2;
+    const uint32_t ha = __umulhi(0xD2511F53u, c0), la = 0xD2511F53u * c0;
     c0 = hb ^ c1 ^ k0;
     c2 = ha ^ c3 ^ k1;
     c1 = lb;
@@ -124,9 +131,43 @@ __device__ __forceinline__ float philox_uniform(uint64_t seed, uint64_t ctr) {
     k0 += 0x9E3779B9u;
     k1 += 0xBB67AE85u;
   }
-  int32_t x = (int32_t)c0;
+  return make_uint4(c0, c1, c2, c3);
+}
+
+// word -> uniform in [0,1): reinterpret as int32, x<0 -> -x-1, times 4.6566127342e-10f
+__device__ __forceinline__ float philox_word_to_uniform(uint32_t w) {
+  int32_t x = (int32_t)w;
   if (x < 0) x = -x - 1;
   return __fmul_rn((float)x, 4.6566127342e-10f);
+}
+
+// Block path: u = f(FIRST word of philox(seed, ctr)).  This is the stream
+// tl.rand(seed, offset) produces, which the reference's block quantizer draws
+// at offset n*K + k (tcfp/kernels.py:415-417).
+__device__ __forceinline__ float philox_uniform(uint64_t seed, uint64_t ctr) {
+  return philox_word_to_uniform(philox4x32_10(seed, ctr).x);
+}
+
+// Per-tensor paths (the reference draws torch.rand_like there, which nothing
+// else can reproduce; the stream is this library's definition): element j
+// takes word (j & 3) of philox(seed, j >> 2), so one generator call serves
+// four elements.  Fills the uniforms of elements base .. base + 3.
+__device__ __forceinline__ void philox_uniform_x4(uint64_t seed, uint64_t base, float u[4]) {
+  const uint4 a = philox4x32_10(seed, base >> 2);
+  const int sh = (int)(base & 3u);
+  if (sh == 0) {
+    u[0] = philox_word_to_uniform(a.x); u[1] = philox_word_to_uniform(a.y);
+    u[2] = philox_word_to_uniform(a.z); u[3] = philox_word_to_uniform(a.w);
+    return;
+  }
+  // a window that straddles two generator calls (stream offsets that are not multiples of four)
+  const uint4 b = philox4x32_10(seed, (base >> 2) + 1);
+  uint32_t w0, w1, w2, w3;
+  if (sh == 1) { w0 = a.y; w1 = a.z; w2 = a.w; w3 = b.x; }
+  else if (sh == 2) { w0 = a.z; w1 = a.w; w2 = b.x; w3 = b.y; }
+  else { w0 = a.w; w1 = b.x; w2 = b.y; w3 = b.z; }
+  u[0] = philox_word_to_uniform(w0); u[1] = philox_word_to_uniform(w1);
+  u[2] = philox_word_to_uniform(w2); u[3] = philox_word_to_uniform(w3);
 }
 
 // ---- stochastic rounding, two variants -------------------------------------

@@ -56,6 +56,14 @@ extern "C" int32_t tcfp_block_dual_gemm_static(const uint8_t* a, const int8_t* e
   if (M <= 0 || N <= 0 || K <= 0 || K % block_size != 0)
     return tcfp::fail(TCFP_ERR_INVALID, "block_dual_gemm_static: bad shape M=%lld N=%lld K=%lld", (long long)M,
                       (long long)N, (long long)K);
+  // everything the GEMM entry point would refuse is refused here, before the first
+  // pack kernel runs: a rejected call must leave the shared scratch as it found it
+  if (out_dtype != TCFP_F32 && out_dtype != TCFP_BF16)
+    return tcfp::fail(TCFP_ERR_INVALID, "block_dual_gemm_static: output must be float32 or bfloat16");
+  if (M > 0x7FFFFFFF || N > 0x7FFFFFFF || K > 0x7FFFFFFF || (K % 16) != 0 || (N % (out_dtype == TCFP_BF16 ? 8 : 4)) != 0 ||
+      (((uintptr_t)a | (uintptr_t)w_hi | (uintptr_t)w_lo | (uintptr_t)out) & 15u))
+    return tcfp::fail(TCFP_ERR_INVALID,
+                      "block_dual_gemm_static: operands need 16-byte aligned base pointers and row pitches");
   const size_t need_a = tcfp_sf_packed_bytes(M, K, block_size);
   const size_t need_w = tcfp_sf_packed_bytes(N, K, block_size);
   if (need_a > kRegionBytes || need_w > kRegionBytes)

@@ -57,11 +57,19 @@ __device__ __forceinline__ uint32_t pack4(uint8_t a, uint8_t b, uint8_t c, uint8
   return (uint32_t)a | ((uint32_t)b << 8) | ((uint32_t)c << 16) | ((uint32_t)d << 24);
 }
 
+// max of a non-negative value over aligned groups of GROUP lanes: non-negative
+// floats order like their bit patterns, so one integer warp-reduce per group
+// replaces a shuffle tree (every lane of the warp takes part, each with its
+// own group's member mask)
 template <int GROUP>
 __device__ __forceinline__ float group_max(float v) {
-#pragma unroll
-  for (int o = GROUP / 2; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
-  return v;
+  if constexpr (GROUP == 32) {
+    return __uint_as_float(__reduce_max_sync(0xFFFFFFFFu, __float_as_uint(v)));
+  } else {
+    const unsigned lane = threadIdx.x & 31u;
+    const unsigned mask = ((1u << GROUP) - 1u) << (lane & ~(unsigned)(GROUP - 1));
+    return __uint_as_float(__reduce_max_sync(mask, __float_as_uint(v)));
+  }
 }
 
 __device__ __forceinline__ float amax4(const f4& x) {
@@ -103,7 +111,7 @@ __device__ __forceinline__ void flush_tile_scales(const int8_t (*s_exp)[kTileRow
 // K1a: block-scaled dual quantizer
 // ---------------------------------------------------------------------------
 template <int BS, bool W_BF16, int MODE>
-__global__ void __launch_bounds__(kThreads, 4)
+__global__ void __launch_bounds__(kThreads, (MODE == TCFP_Q_NONE) ? 5 : 4)
 dual_quantize_block_kernel(const void* __restrict__ w, float* err, uint8_t* __restrict__ w_hi,
                            uint8_t* __restrict__ w_lo, int8_t* __restrict__ exp_hi,
                            int8_t* __restrict__ exp_lo, uint8_t* __restrict__ sf_hi,
@@ -151,11 +159,13 @@ dual_quantize_block_kernel(const void* __restrict__ w, float* err, uint8_t* __re
       const uint32_t ph = encode_fp8x2<false>(__fmul_rn(wc.v[0], fwd_hi), __fmul_rn(wc.v[1], fwd_hi)) |
                           (encode_fp8x2<false>(__fmul_rn(wc.v[2], fwd_hi), __fmul_rn(wc.v[3], fwd_hi)) << 16);
       f4 hdq, res;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        hdq.v[i] = __fmul_rn(decode_fp8_fast<false>(ph >> (8 * i)), inv_hi);
-        res.v[i] = __fsub_rn(wc.v[i], hdq.v[i]);
+      {
+        const float2 d01 = decode_fp8x2<false>(ph), d23 = decode_fp8x2<false>(ph >> 16);
+        hdq.v[0] = __fmul_rn(d01.x, inv_hi); hdq.v[1] = __fmul_rn(d01.y, inv_hi);
+        hdq.v[2] = __fmul_rn(d23.x, inv_hi); hdq.v[3] = __fmul_rn(d23.y, inv_hi);
       }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) res.v[i] = __fsub_rn(wc.v[i], hdq.v[i]);
       // --- W_lo
       const float amax_lo = group_max<GROUP>(amax4(res));
       const bool zero_res = amax_lo < kAmaxFloor;
@@ -185,10 +195,12 @@ dual_quantize_block_kernel(const void* __restrict__ w, float* err, uint8_t* __re
           // value -128 dequantizes with 2^-128; its codes are all zero.
           const float inv_lo = zero_res ? exp2_int(-128) : exp2_int(e_lo);
           f4 en;
+          const float2 l01 = decode_fp8x2<false>(pl), l23 = decode_fp8x2<false>(pl >> 16);
+          const float ld[4] = {l01.x, l01.y, l23.x, l23.y};
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             float t = __fsub_rn(wv[s].v[i], hdq.v[i]);
-            en.v[i] = __fsub_rn(t, __fmul_rn(decode_fp8_fast<false>(pl >> (8 * i)), inv_lo));
+            en.v[i] = __fsub_rn(t, __fmul_rn(ld[i], inv_lo));
           }
           store4f(err, idx, en);
         }
@@ -210,22 +222,45 @@ dual_quantize_block_kernel(const void* __restrict__ w, float* err, uint8_t* __re
 // One 128-bit load per lane: 4 float32 or 8 bfloat16 values, so a tile is 512
 // or 1024 columns wide and a scale block is a group of BS/4 or BS/8 lanes.
 // ---------------------------------------------------------------------------
-template <int BS, bool X_BF16, bool E5M2>
+// With COLSUM the kernel also produces the column sums of x (the bias
+// gradient when x is the output gradient, tcfp/nn/__init__.py:558, 753, which
+// the reference takes in a separate full pass): a CTA walks kColsumRowTiles
+// row tiles, keeps per-thread partial sums of its columns, folds the eight
+// warps' partials in a fixed order and writes one row of `partial`
+// ((row groups) x C floats); colsum_reduce_kernel adds the row groups, again
+// in a fixed order, so the result does not depend on scheduling.
+constexpr int kColsumRowTiles = 8;
+
+template <int BS, bool X_BF16, bool E5M2, bool COLSUM = false>
 __global__ void __launch_bounds__(kThreads)
 quantize_block_kernel(const void* __restrict__ x, uint8_t* __restrict__ out, int8_t* __restrict__ exps,
-                      uint8_t* __restrict__ sf, __nv_bfloat16* __restrict__ deq, int64_t R, int64_t C) {
+                      uint8_t* __restrict__ sf, __nv_bfloat16* __restrict__ deq, int64_t R, int64_t C,
+                      float* __restrict__ partial = nullptr) {
   constexpr int VEC = X_BF16 ? 8 : 4;
   constexpr int GROUP = BS / VEC;
   constexpr int SEG = 32 * VEC;             // columns one warp covers per load
   constexpr int TILE_COLS = 4 * SEG;
   constexpr int kBlocksPerTile = TILE_COLS / BS;
+  constexpr int RT = COLSUM ? kColsumRowTiles : 1;
   __shared__ int8_t s_e[kBlocksPerTile][kTileRows];
+  __shared__ float s_sum[COLSUM ? kThreads / 32 : 1][COLSUM ? TILE_COLS : 1];
 
   const int64_t tiles_c = (C + TILE_COLS - 1) / TILE_COLS;
-  const int64_t row0 = (int64_t)(blockIdx.x / tiles_c) * kTileRows;
+  const int64_t row_group = (int64_t)(blockIdx.x / tiles_c);
   const int64_t col0 = (int64_t)(blockIdx.x % tiles_c) * TILE_COLS;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float acc[COLSUM ? 4 : 1][COLSUM ? VEC : 1];
+  if constexpr (COLSUM) {
+#pragma unroll
+    for (int s = 0; s < 4; ++s)
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) acc[s][i] = 0.f;
+  }
 
+#pragma unroll 1
+  for (int rt = 0; rt < RT; ++rt) {
+  const int64_t row0 = (row_group * RT + rt) * kTileRows;
+  if (COLSUM && row0 >= R) break;
 #pragma unroll 1
   for (int rr = 0; rr < 4; ++rr) {
     const int r_local = warp * 4 + rr;
@@ -260,6 +295,10 @@ quantize_block_kernel(const void* __restrict__ x, uint8_t* __restrict__ out, int
       float am = 0.f;
 #pragma unroll
       for (int i = 0; i < VEC; ++i) am = fmaxf(am, fabsf(xv[s][i]));
+      if constexpr (COLSUM) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) acc[s][i] = __fadd_rn(acc[s][i], xv[s][i]);
+      }
       const int e = block_exponent_fast<E5M2>(group_max<GROUP>(am));
       const float fwd = exp2_int(-e), inv = exp2_int(e);
       uint32_t pc[VEC / 4];
@@ -289,6 +328,70 @@ quantize_block_kernel(const void* __restrict__ x, uint8_t* __restrict__ out, int
   }
   __syncthreads();
   flush_tile_scales<BS, TILE_COLS>(s_e, exps, sf, R, C, row0, col0);
+  if constexpr (COLSUM) __syncthreads();      // the next row tile rewrites s_e
+  }
+  if constexpr (COLSUM) {
+#pragma unroll
+    for (int s = 0; s < 4; ++s)
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) s_sum[warp][s * SEG + lane * VEC + i] = acc[s][i];
+    __syncthreads();
+    for (int c = threadIdx.x; c < TILE_COLS; c += kThreads) {
+      float t = s_sum[0][c];
+#pragma unroll
+      for (int w = 1; w < kThreads / 32; ++w) t = __fadd_rn(t, s_sum[w][c]);
+      if (col0 + c < C) partial[row_group * C + col0 + c] = t;
+    }
+  }
+}
+
+// Per-tensor path: one read of x yields its amax (the quantizer's scale) and
+// the column sums.  256 rows x 512 columns per CTA, two rows in flight per
+// column group.
+constexpr int kAcRows = 256;
+constexpr int kAcCols = 512;
+
+template <bool X_BF16>
+__global__ void __launch_bounds__(kThreads)
+amax_colsum_kernel(const void* __restrict__ x, int64_t R, int64_t C, unsigned int* amax_word,
+                   float* __restrict__ partial) {
+  __shared__ float s_part[kAcCols];
+  __shared__ float s_m[kThreads / 32];
+  const int cl = threadIdx.x & 127, rl = threadIdx.x >> 7;
+  const int64_t col = (int64_t)blockIdx.x * kAcCols + 4 * cl;
+  const int64_t r_begin = (int64_t)blockIdx.y * kAcRows;
+  const int64_t r_end = r_begin + kAcRows < R ? r_begin + kAcRows : R;
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, m = 0.f;
+  if (col < C) {
+#pragma unroll 4
+    for (int64_t r = r_begin + rl; r < r_end; r += 2) {
+      const f4 v = load4<X_BF16>(x, (size_t)r * C + col);
+      a0 = __fadd_rn(a0, v.v[0]); a1 = __fadd_rn(a1, v.v[1]); a2 = __fadd_rn(a2, v.v[2]); a3 = __fadd_rn(a3, v.v[3]);
+      m = fmaxf(m, amax4(v));
+    }
+  }
+  if (rl == 1) { s_part[4 * cl] = a0; s_part[4 * cl + 1] = a1; s_part[4 * cl + 2] = a2; s_part[4 * cl + 3] = a3; }
+  m = group_max<32>(m);
+  if ((threadIdx.x & 31) == 0) s_m[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (rl == 0 && col < C) {
+    float* dst = partial + (size_t)blockIdx.y * C + col;
+    dst[0] = __fadd_rn(a0, s_part[4 * cl]); dst[1] = __fadd_rn(a1, s_part[4 * cl + 1]);
+    dst[2] = __fadd_rn(a2, s_part[4 * cl + 2]); dst[3] = __fadd_rn(a3, s_part[4 * cl + 3]);
+  }
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < kThreads / 32; ++i) m = fmaxf(m, s_m[i]);
+    atomicMax(amax_word, __float_as_uint(m));
+  }
+}
+
+// out[c] = sum over the row groups of partial[g][c], in order
+__global__ void colsum_reduce_kernel(const float* __restrict__ partial, int64_t groups, int64_t C, float* __restrict__ out) {
+  const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float t = 0.f;
+  for (int64_t g = 0; g < groups; ++g) t = __fadd_rn(t, partial[g * C + c]);
+  out[c] = t;
 }
 
 // exponent plane -> packed chunks, one thread per (row, k_group)
@@ -423,10 +526,12 @@ pt_quantize_kernel(const void* __restrict__ x, uint8_t* __restrict__ out, float*
       uint32_t pq;
       if constexpr (SR && !E5M2) {
         uint8_t q[4];
+        float un[4];
+        philox_uniform_x4(seed, offset + (uint64_t)v * 4u, un);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const float xs = clampf(__fmul_rn(xv[u].v[i], scale), FMAX);
-          q[i] = sr_tensor_e4m3(xs, philox_uniform(seed, offset + (uint64_t)v * 4u + (uint64_t)i));
+          q[i] = sr_tensor_e4m3(xs, un[i]);
         }
         pq = pack4(q[0], q[1], q[2], q[3]);
       } else {
@@ -531,6 +636,8 @@ pt_lo_kernel(const void* __restrict__ w, float* err, uint8_t* w_hi, uint8_t* __r
       int64_t v = c * kPtChunk + u * kThreads + threadIdx.x;
       uint8_t qh[4], ql[4];
       f4 en;
+      float un[4];
+      if constexpr (MODE == TCFP_Q_SRR) philox_uniform_x4(seed, offset + (uint64_t)v * 4u, un);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         float wc = HAS_ERR ? __fadd_rn(xv[u].v[i], ev[u].v[i]) : xv[u].v[i];
@@ -541,7 +648,7 @@ pt_lo_kernel(const void* __restrict__ w, float* err, uint8_t* w_hi, uint8_t* __r
         if constexpr (FUSED_HI) m = fmaxf(m, fabsf(r));
         float xs = clampf(__fmul_rn(r, sc_lo), kE4M3Max);
         if constexpr (MODE == TCFP_Q_SRR) {
-          ql[i] = sr_tensor_e4m3(xs, philox_uniform(seed, offset + (uint64_t)v * 4u + (uint64_t)i));
+          ql[i] = sr_tensor_e4m3(xs, un[i]);
         } else {
           ql[i] = encode_fp8<false>(xs);
         }
@@ -750,6 +857,56 @@ extern "C" int32_t tcfp_quantize(const void* x, int32_t x_dtype, uint8_t* out, v
     DISPATCH_BOOL(bf16, X_BF16, DISPATCH_BOOL(e5m2, E5M2,
       pt_quantize_kernel<X_BF16, E5M2, false><<<grid, kThreads, 0, stream>>>(x, out, (float*)scale_out, nvec, ws, amax_in, scale_in, 0, 0)));
   }
+  CUDA_TRY(cudaGetLastError());
+  return TCFP_OK;
+}
+
+extern "C" size_t tcfp_colsum_workspace_bytes(int64_t R, int64_t C) {
+  if (R <= 0 || C <= 0) return 0;
+  // one row of partial sums per 256 input rows (both scaling modes), plus the amax words
+  return (size_t)(((R + 255) / 256) * C) * sizeof(float) + 256;
+}
+
+extern "C" int32_t tcfp_quantize_colsum(const void* x, int32_t x_dtype, uint8_t* out, void* scale_out, uint8_t* sf_out,
+                                        int64_t R, int64_t C, int32_t block_size, int32_t fmt, float* colsum_out,
+                                        void* workspace, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (!x || !out || !scale_out || !colsum_out || !workspace) return fail(TCFP_ERR_INVALID, "quantize_colsum: NULL pointer");
+  if (R <= 0 || C <= 0) return fail(TCFP_ERR_INVALID, "quantize_colsum: empty shape (%lld, %lld)", (long long)R, (long long)C);
+  if (x_dtype != TCFP_F32 && x_dtype != TCFP_BF16) return fail(TCFP_ERR_INVALID, "quantize_colsum: input must be float32 or bfloat16");
+  if (fmt != TCFP_E4M3 && fmt != TCFP_E5M2) return fail(TCFP_ERR_INVALID, "quantize_colsum: unknown FP8 format %d", fmt);
+  const bool bf16 = (x_dtype == TCFP_BF16), e5m2 = (fmt == TCFP_E5M2);
+  if (C % 4 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)out & 7) || ((uintptr_t)workspace & 15) || (bf16 && C % 8 != 0))
+    return fail(TCFP_ERR_INVALID, "quantize_colsum: tensors must be contiguous and 16-byte aligned, C %% 4 == 0 (8 for bfloat16)");
+  float* partial = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(workspace) + 256);
+  unsigned int* ws = reinterpret_cast<unsigned int*>(workspace);
+  int64_t groups;
+  if (block_size != 0) {
+    if (block_size != 32 && block_size != 64 && block_size != 128)
+      return fail(TCFP_ERR_INVALID, "block_size must be 32, 64, or 128, got %d", block_size);
+    if (C % block_size != 0)
+      return fail(TCFP_ERR_INVALID, "K (%lld) must be divisible by block_size (%d)", (long long)C, block_size);
+    if (sf_out && ((C / block_size) % 4 != 0))
+      CUDA_TRY(cudaMemsetAsync(sf_out, 127, tcfp_sf_packed_bytes(R, C, block_size), stream));
+    const int64_t tile_cols = bf16 ? 2 * kTileCols : kTileCols;
+    groups = (R + kTileRows * kColsumRowTiles - 1) / (kTileRows * kColsumRowTiles);
+    const int64_t ctas = groups * ((C + tile_cols - 1) / tile_cols);
+    if (ctas > 0x7FFFFFFF) return fail(TCFP_ERR_UNSUPPORTED, "quantize_colsum: tensor too large");
+    DISPATCH_BS(block_size, DISPATCH_BOOL(bf16, X_BF16, DISPATCH_BOOL(e5m2, E5M2,
+      quantize_block_kernel<BS, X_BF16, E5M2, true><<<(unsigned)ctas, kThreads, 0, stream>>>(
+          x, out, (int8_t*)scale_out, sf_out, nullptr, R, C, partial))));
+  } else {
+    groups = (R + kAcRows - 1) / kAcRows;
+    if (groups > 65535) return fail(TCFP_ERR_UNSUPPORTED, "quantize_colsum: more than 16M rows");
+    CUDA_TRY(cudaMemsetAsync(ws, 0, 8, stream));
+    const dim3 grid((unsigned)((C + kAcCols - 1) / kAcCols), (unsigned)groups, 1);
+    DISPATCH_BOOL(bf16, X_BF16, amax_colsum_kernel<X_BF16><<<grid, kThreads, 0, stream>>>(x, R, C, ws, partial));
+    const int64_t nvec = R * C / 4;
+    DISPATCH_BOOL(bf16, X_BF16, DISPATCH_BOOL(e5m2, E5M2,
+      pt_quantize_kernel<X_BF16, E5M2, false><<<flat_grid(nvec), kThreads, 0, stream>>>(
+          x, out, (float*)scale_out, nvec, ws, nullptr, nullptr, 0, 0)));
+  }
+  colsum_reduce_kernel<<<(unsigned)((C + 255) / 256), 256, 0, stream>>>(partial, groups, C, colsum_out);
   CUDA_TRY(cudaGetLastError());
   return TCFP_OK;
 }

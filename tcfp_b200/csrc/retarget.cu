@@ -96,8 +96,8 @@ block_retarget_kernel(const uint8_t* __restrict__ codes_hi, const uint8_t* __res
       const int e = (int)s_e[cb][4 * rw + rr];
       const int shift = e - t;                    // <= 0 for live rows
       const float f = (e == -128 || shift < -126) ? 0.f : exp2_int(shift);
-      w[rr] = encode_fp8x2<false>(decode_fp8_fast<false>(raw) * f, decode_fp8_fast<false>(raw >> 8) * f) |
-              (encode_fp8x2<false>(decode_fp8_fast<false>(raw >> 16) * f, decode_fp8_fast<false>(raw >> 24) * f) << 16);
+      const float2 d01 = decode_fp8x2<false>(raw), d23 = decode_fp8x2<false>(raw >> 16);
+      w[rr] = encode_fp8x2<false>(d01.x * f, d01.y * f) | (encode_fp8x2<false>(d23.x * f, d23.y * f) << 16);
     }
     // byte transpose: word j gathers byte j of the four rows
     const uint32_t a01 = __byte_perm(w[0], w[1], 0x5140), b01 = __byte_perm(w[0], w[1], 0x7362);

@@ -179,10 +179,16 @@ def bf16_weight_grad(grad: torch.Tensor, act_bf16: torch.Tensor) -> torch.Tensor
 # block quantizers (tcfp/kernels.py:1675-1875)
 # ---------------------------------------------------------------------------
 
-def block_quantize_fp8(tensor, block_size=128, fp8_dtype=torch.float8_e4m3fn, *, want_bf16=False):
+def _colsum_workspace(R: int, C: int, device) -> torch.Tensor:
+    return torch.empty(_C.load().tcfp_colsum_workspace_bytes(R, C), dtype=torch.uint8, device=device)
+
+
+def block_quantize_fp8(tensor, block_size=128, fp8_dtype=torch.float8_e4m3fn, *, want_bf16=False, want_colsum=False):
     """Per-block FP8 quantization (tcfp/kernels.py:1675-1722).  Returns
     ``(fp8 (M,K), int8 exponents (K // bs, M))``; with ``want_bf16`` a third
-    tensor holds the dequantized values as bf16."""
+    tensor holds the dequantized values as bf16; with ``want_colsum`` a third
+    tensor holds the FP32 column sums of the input (the bias gradient when the
+    input is an output gradient), accumulated in the same pass."""
     M, K = tensor.shape
     assert K % block_size == 0, f"K ({K}) must be divisible by block_size ({block_size})"
     assert tensor.is_contiguous(), "input must be contiguous"
@@ -190,6 +196,14 @@ def block_quantize_fp8(tensor, block_size=128, fp8_dtype=torch.float8_e4m3fn, *,
     out = torch.empty((M, K), device=tensor.device, dtype=fp8_dtype)
     scales = torch.empty((num_kb, M), device=tensor.device, dtype=torch.int8)
     sf = _alloc_sf(M, K, block_size, tensor.device)
+    if want_colsum:
+        assert not want_bf16, "want_colsum and want_bf16 are separate variants"
+        colsum = torch.empty(K, device=tensor.device, dtype=torch.float32)
+        _C.check(_C.load().tcfp_quantize_colsum(
+            _C.ptr(tensor), _C.dtype_code(tensor), _C.ptr(out), _C.ptr(scales), _C.ptr(sf), M, K, block_size, _fmt(out),
+            _C.ptr(colsum), _C.ptr(_colsum_workspace(M, K, tensor.device)), _C.stream()))
+        _attach_sf(scales, sf, block_size)
+        return out, scales, colsum
     deq = torch.empty((M, K), device=tensor.device, dtype=torch.bfloat16) if want_bf16 else None
     _C.check(_C.load().tcfp_quantize(
         _C.ptr(tensor), _C.dtype_code(tensor), _C.ptr(out), _C.ptr(scales), _C.ptr(sf), _C.ptr(deq),

@@ -5,6 +5,9 @@ sizes).  Used to time single kernels and as the target of ncu captures:
     python -m tcfp_b200.microbench block  [N]   # block-scaled dual GEMM fwd + dX, N^3, block 32/64/128
     python -m tcfp_b200.microbench quant  [N]   # block and per-tensor quantizers on N x N
     python -m tcfp_b200.microbench lib    [N]   # library comparators: torch._scaled_mm, bf16 matmul
+    python -m tcfp_b200.microbench qvar   [N]   # the ALU-heavy quantizer variants only (no error buffer, stochastic
+                                                # residual, per-tensor stochastic), few launches: the ncu target
+    python -m tcfp_b200.microbench dx     [N]   # block dX: re-targeting pass + FP8 GEMM, and the exact bf16 route
 """
 from __future__ import annotations
 
@@ -60,9 +63,9 @@ def block(n: int) -> None:
         a, sa = block_quantize_fp8(x, bs)
         ms = timeit(lambda: fused_block_scaled_dual_gemm_forward(a, hi, lo, sa, sh, sl, bs))
         print(f"block-{bs} dual GEMM fwd {n}^3: {ms:.3f} ms  {4 * n**3 / ms / 1e9:.0f} TFLOP/s (both products)")
-        gq, sg, gb = block_quantize_fp8(gy, bs, torch.float8_e5m2, want_bf16=True)
-        ms = timeit(lambda: fused_block_scaled_backward_dx(gq, hi, lo, sg, sh, sl, bs, grad_bf16=gb))
-        print(f"block-{bs} dX (dequant + bf16 GEMM) {n}^3: {ms:.3f} ms  {4 * n**3 / ms / 1e9:.0f} TFLOP/s (both products)")
+        gq, sg = block_quantize_fp8(gy, bs, torch.float8_e5m2)
+        ms = timeit(lambda: fused_block_scaled_backward_dx(gq, hi, lo, sg, sh, sl, bs))
+        print(f"block-{bs} dX (FP8, weight re-targeted once) {n}^3: {ms:.3f} ms  {4 * n**3 / ms / 1e9:.0f} TFLOP/s (both products)")
 
 
 def quant(n: int) -> None:
@@ -95,6 +98,35 @@ def quant(n: int) -> None:
     report("to_fp8_e5m2 f32 (2 passes)", timeit(lambda: to_fp8_e5m2(gy)), 5)
 
 
+def qvar(n: int) -> None:
+    from .core import dual_quantize_per_tensor
+    from .kernels import fused_dual_quantize_fp8
+
+    w = torch.randn(n, n, device=DEV) * 0.02
+    e = n * n
+    for name, fn in (("dual_quantize block-64 no EF", lambda: fused_dual_quantize_fp8(w, 64, None)),
+                     ("dual_quantize block-64 SRR", lambda: fused_dual_quantize_fp8(w, 64, None, True, seed=1)),
+                     ("dual_quantize per-tensor SRR", lambda: dual_quantize_per_tensor(w, None, srr=True, seed=1))):
+        ms = timeit(fn, iters=5, warmup=2)
+        print(f"{name:<34s} {ms * 1e3:8.1f} us  {6 * e / ms / 1e6:7.0f} GB/s (6 B/elem algorithmic)")
+
+
+def dx(n: int) -> None:
+    from .kernels import block_quantize_fp8, block_retarget, fused_block_scaled_backward_dx, fused_dual_quantize_fp8
+
+    w = torch.randn(n, n, device=DEV) * 0.02
+    gy = torch.randn(n, n, device=DEV)
+    for bs in (32, 64, 128):
+        hi, lo, sh, sl = fused_dual_quantize_fp8(w, bs)
+        gq, sg = block_quantize_fp8(gy, bs, torch.float8_e5m2)
+        ms_r = timeit(lambda: block_retarget(hi, lo, sh, sl, bs), iters=10)
+        fused_block_scaled_backward_dx(gq, hi, lo, sg, sh, sl, bs)
+        ms_g = timeit(lambda: fused_block_scaled_backward_dx(gq, hi, lo, sg, sh, sl, bs), iters=10)
+        ms_b = timeit(lambda: fused_block_scaled_backward_dx(gq, hi, lo, sg, sh, sl, bs, exact_bf16=True), iters=10)
+        print(f"block-{bs} dX {n}^3: retarget {ms_r * 1e3:.1f} us ({4 * n * n / ms_r / 1e6:.0f} GB/s) + FP8 GEMM {ms_g:.3f} ms "
+              f"({4 * n**3 / ms_g / 1e9:.0f} TFLOP/s); exact bf16 route {ms_b:.3f} ms")
+
+
 def lib(n: int) -> None:
     a, hi, lo = _fp8(n, n), _fp8(n, n), _fp8(n, n)
     s = torch.ones(1, device=DEV)
@@ -115,4 +147,4 @@ def lib(n: int) -> None:
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     size = int(sys.argv[2]) if len(sys.argv) > 2 else 8192
-    {"gemm": gemm, "block": block, "quant": quant, "lib": lib}[what](size)
+    {"gemm": gemm, "block": block, "quant": quant, "lib": lib, "qvar": qvar, "dx": dx}[what](size)

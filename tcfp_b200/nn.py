@@ -26,6 +26,7 @@ from .core import (
     nf_aware_target_max,
     to_fp8_e4m3,
     to_fp8_e5m2,
+    to_fp8_e5m2_with_colsum,
 )
 from .kernels import (
     bf16_weight_grad,
@@ -206,7 +207,14 @@ class _TCFP12TensorCoreFunction(torch.autograd.Function):
         g2d = _flat2d(grad_output)
         if g2d.dtype not in (torch.float32, torch.bfloat16):
             g2d = g2d.float()
-        grad_fp8, grad_inv = to_fp8_e5m2(g2d)                    # always fresh (:494)
+        # always fresh (:494); with a bias its gradient (the column sums, :558) comes out of the same passes
+        grad_bias = None
+        if ctx.has_bias and g2d.shape[1] % 8 == 0:
+            grad_fp8, grad_inv, grad_bias = to_fp8_e5m2_with_colsum(g2d)
+        else:
+            grad_fp8, grad_inv = to_fp8_e5m2(g2d)
+            if ctx.has_bias:
+                grad_bias = g2d.float().sum(dim=0)
         grad_input = fused_dual_gemm_backward_dx(grad_fp8, w_hi, w_lo, grad_inv, inv_hi, inv_lo,
                                                  out_dtype=ctx.dx_dtype)
         dx_pending = ctx.dx_hook(grad_input) if ctx.dx_hook is not None else None   # overlaps the dW GEMM below
@@ -218,7 +226,6 @@ class _TCFP12TensorCoreFunction(torch.autograd.Function):
                 grad_weight = g2d.float().t() @ saved_act.float()    # (:541-542)
         else:
             grad_weight = fp8_weight_grad(grad_fp8, saved_act, grad_inv, act_inv)   # (:546-555)
-        grad_bias = g2d.float().sum(dim=0) if ctx.has_bias else None
         _wait_all([dx_pending])
         return (grad_input, grad_weight, grad_bias) + (None,) * 13
 
@@ -295,7 +302,11 @@ class _TCFP12BlockScaledFunction(torch.autograd.Function):
             g2d = g2d.float()
         # E5M2 block quantize of the gradient along D_out (:724-726); dX on the FP8 block-scaled MMA against
         # the weight re-targeted for this contraction (once per weight version, kept on w_hi)
-        grad_fp8, grad_scales = block_quantize_fp8(g2d, bs, torch.float8_e5m2)
+        if ctx.has_bias:        # the bias gradient (column sums, :753) rides the quantizer's pass
+            grad_fp8, grad_scales, grad_bias = block_quantize_fp8(g2d, bs, torch.float8_e5m2, want_colsum=True)
+        else:
+            grad_fp8, grad_scales = block_quantize_fp8(g2d, bs, torch.float8_e5m2)
+            grad_bias = None
         grad_input = fused_block_scaled_backward_dx(grad_fp8, w_hi, w_lo, grad_scales, s_hi, s_lo, bs,
                                                     out_dtype=ctx.dx_dtype)
         dx_pending = ctx.dx_hook(grad_input) if ctx.dx_hook is not None else None   # overlaps the dW GEMM below
@@ -309,7 +320,6 @@ class _TCFP12BlockScaledFunction(torch.autograd.Function):
         else:
             # the saved codes dequantize exactly to bf16; the FP32 gradient goes in as bf16 head + tail
             grad_weight = bf16_weight_grad(g2d, block_dequantize_bf16(saved_act, act_scales, bs))
-        grad_bias = g2d.float().sum(dim=0) if ctx.has_bias else None
         _wait_all([dx_pending])
         return (grad_input, grad_weight, grad_bias) + (None,) * 12
 
@@ -326,8 +336,10 @@ class TCFPLinear(nn.Module):
     training policies mutate them live.  ``use_fused_kernel`` and
     ``use_cuda_ext`` are accepted for compatibility: there is exactly one
     backend here.  Additional keywords: ``srr_seed`` seeds the stochastic
-    residual stream (element ``n*K+k`` of forward call ``i`` draws
-    ``philox(seed, i*N*K + n*K + k)``); ``out_dtype=torch.bfloat16`` makes the
+    residual stream (element ``n*K+k`` of forward call ``i`` is stream position
+    ``j = i*N*K + n*K + k``: ``philox(seed, j)[0]`` with block scaling -- the
+    reference kernel's ``tl.rand`` stream -- and word ``j & 3`` of
+    ``philox(seed, j >> 2)`` with per-tensor scaling); ``out_dtype=torch.bfloat16`` makes the
     GEMM epilogue write bf16 (the reference always returns FP32).
     """
 

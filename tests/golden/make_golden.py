@@ -56,7 +56,7 @@ for name, (seed, shape, dtype) in CAST_CASES.items():
     out[f"cast/{name}/e5m2"], out[f"cast/{name}/e5m2_inv"] = u8(q), i32(inv)
     # stochastic rounding under the seed/offset contract
     scaled = (x.float() * (448.0 / x.float().abs().max())).clamp(-448, 448)
-    rand = O.philox_uniform(seed, 17, scaled.numel()).reshape(scaled.shape)
+    rand = O.philox_uniform_packed(seed, 17, scaled.numel()).reshape(scaled.shape)
     orig = torch.rand_like
     rcore.torch.rand_like = lambda t, *a, **k: rand.to(t.dtype)
     try:
@@ -67,14 +67,14 @@ for name, (seed, shape, dtype) in CAST_CASES.items():
 
 class _PatchedRand:
     """Feeds the reference's ``torch.rand_like`` the contract uniforms:
-    call ``i`` of a step draws philox(seed, offset_i + element)."""
+    call ``i`` of a step draws elements ``offset_i + element`` of the packed per-tensor stream."""
 
     def __init__(self, seed):
         self.seed = seed
         self.offset = 0
 
     def __call__(self, t, *a, **k):
-        r = O.philox_uniform(self.seed, self.offset, t.numel()).reshape(t.shape).to(t.dtype)
+        r = O.philox_uniform_packed(self.seed, self.offset, t.numel()).reshape(t.shape).to(t.dtype)
         self.offset += t.numel()
         return r
 

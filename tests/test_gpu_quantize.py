@@ -195,7 +195,7 @@ def test_to_fp8_casts_bit_exact(dtype):
     q, inv = O.to_fp8_e4m3(x, scale=scale)
     gq, ginv = to_fp8_e4m3(x.to(DEV), scale=scale.to(DEV))
     assert torch.equal(bits(ginv), bits(inv)) and torch.equal(u8(gq), u8(q))
-    rand = O.philox_uniform(5, 3, x.numel()).reshape(x.shape)
+    rand = O.philox_uniform_packed(5, 3, x.numel()).reshape(x.shape)
     q, inv = O.to_fp8_e4m3_sr(x, rand)
     gq, ginv = to_fp8_e4m3_sr(x.to(DEV), seed=5, offset=3)
     assert torch.equal(bits(ginv), bits(inv)) and torch.equal(u8(gq), u8(q))
@@ -219,3 +219,29 @@ def test_pack_scales_layout(lib):
             assert int(sf[off]) == (0 if e == -128 else e + 127)
     # tail blocks of the last K group hold a neutral scale
     assert int(sf[(0 * k_groups + 1) * 512 + 0 * 16 + 0 * 4 + 2]) == 127
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("R,C", [(1000, 384), (4096, 1024), (257, 2048), (31, 128)])
+def test_gradient_quantizers_with_fused_bias_gradient(R, C, dtype):
+    """The column sums (bias gradient, tcfp/nn/__init__.py:558, 753) come out
+    of the gradient quantizers' own passes: same codes and scales as the plain
+    quantizers bit for bit, sums within 1e-5 of a float64 sum, and identical
+    bits on a repeated call (fixed summation order)."""
+    from tcfp_b200.core import to_fp8_e5m2, to_fp8_e5m2_with_colsum
+    from tcfp_b200.kernels import block_quantize_fp8
+
+    g = (acts(90, R, C, torch.float32) * 3.0 + 0.25).to(dtype).to(DEV)
+    want = g.double().sum(dim=0)
+    scale = g.double().abs().sum(dim=0).clamp(min=1e-30)
+    q, inv = to_fp8_e5m2(g)
+    q2, inv2, cs = to_fp8_e5m2_with_colsum(g)
+    assert torch.equal(u8(q2), u8(q)) and torch.equal(bits(inv2), bits(inv))
+    assert float(((cs.double() - want).abs() / scale).max()) <= 1e-5
+    assert torch.equal(bits(to_fp8_e5m2_with_colsum(g)[2]), bits(cs))
+    for bs in (32, 128):
+        q, e = block_quantize_fp8(g, bs, torch.float8_e5m2)
+        q2, e2, cs = block_quantize_fp8(g, bs, torch.float8_e5m2, want_colsum=True)
+        assert torch.equal(u8(q2), u8(q)) and torch.equal(e2, e)
+        assert float(((cs.double() - want).abs() / scale).max()) <= 1e-5
+        assert torch.equal(bits(block_quantize_fp8(g, bs, torch.float8_e5m2, want_colsum=True)[2]), bits(cs))

@@ -35,7 +35,7 @@ def test_casts_match_reference_bits(name):
     q, inv = O.to_fp8_e5m2(x)
     assert np.array_equal(u8(q), GOLD[f"cast/{name}/e5m2"]) and np.array_equal(i32(inv), GOLD[f"cast/{name}/e5m2_inv"])
     scaled = (x.float() * (448.0 / x.float().abs().max())).clamp(-448, 448)
-    rand = O.philox_uniform(seed, 17, scaled.numel()).reshape(scaled.shape)
+    rand = O.philox_uniform_packed(seed, 17, scaled.numel()).reshape(scaled.shape)
     assert np.array_equal(u8(O.stochastic_round_to_fp8_e4m3(scaled, rand)), GOLD[f"cast/{name}/sr"])
 
 
@@ -82,6 +82,16 @@ def test_philox_known_answers():
     assert torch.equal(O.philox_uniform(123, 100, 16), O.philox_uniform(123, 0, 116)[100:])
     # high counter word is used
     assert not torch.equal(O.philox_uniform(1, 0, 8), O.philox_uniform(1, 1 << 32, 8))
+    # all four output words (Random123 known-answer vector, zero counter and key)
+    words = O.philox4x32_10(0, np.array([0], dtype=np.uint64), all_words=True)[:, 0]
+    assert [int(w) for w in words] == [0x6627E8D5, 0xE169C58D, 0xBC57AC4C, 0x9B00DBD8]
+    # packed per-tensor stream: element j is word j & 3 of call j >> 2, at any offset
+    full = O.philox_uniform_packed(77, 0, 64)
+    calls = O.philox4x32_10(77, np.arange(16, dtype=np.uint64), all_words=True)
+    assert torch.equal(full, torch.from_numpy(O._word_to_uniform(np.ascontiguousarray(calls.T.reshape(-1)))))
+    assert torch.equal(full[::4], O.philox_uniform(77, 0, 16))
+    for off, n in ((1, 7), (3, 13), (17, 40), (4, 8)):
+        assert torch.equal(O.philox_uniform_packed(77, off, n), full[off:off + n])
 
 
 @pytest.mark.parametrize("bs", [32, 64, 128])

@@ -31,8 +31,8 @@ def test_quantizers_match_reference_triton_kernels(name):
 @pytest.mark.parametrize("name", list(BLOCK_CASES))
 def test_gemms_match_reference_triton_kernels(name):
     """Forward and dX on the reference kernels' own quantized operands,
-    against the reference kernels' FP32 outputs (1e-3 relative Frobenius, the
-    tolerance of the north-star; measured ~1e-7)."""
+    against the reference kernels' FP32 outputs (tolerance: 1e-3 relative
+    Frobenius error; measured ~1e-7)."""
     from tcfp_b200.kernels import fused_block_scaled_dual_gemm_backward_dx, fused_block_scaled_dual_gemm_forward
 
     bs = BLOCK_CASES[name]["bs"]
