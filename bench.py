@@ -226,6 +226,24 @@ def _reference_gpu(dev, a, s_a, w_hi, w_lo, s_hi, s_lo, x, w, ours_ms: float | N
         if rc.is_cuda_ext_available():
             out["cublaslt_ext_per_tensor"] = entry(t(lambda: rc.cuda_ext_dual_gemm_forward(p_a, p_hi, p_lo, i_a, i_hi, i_lo)))
         out["ours_per_tensor_dual_gemm"] = entry(t(lambda: fused_dual_gemm_forward(p_a, p_hi, p_lo, i_a, i_hi, i_lo)))
+        # the small-N case the reference fuses its activation quantizer into (tcfp/nn/__init__.py:620-640):
+        # its fused Triton kernel against this library's quantize + GEMM pair, same inputs
+        if rk.is_triton_available():
+            from tcfp_b200.kernels import fused_act_quant_dual_gemm_forward, fused_dual_quantize_fp8
+
+            small = {}
+            m_tok, k_in = 32768, 4096
+            xa = torch.randn(m_tok, k_in, device=dev, dtype=torch.bfloat16)
+            for n_out in (128, 256, 512):
+                ws = torch.randn(n_out, k_in, device=dev) * 0.02
+                hi_s, lo_s, sh_s, sl_s = fused_dual_quantize_fp8(ws, BS)
+                rk.fused_act_quant_dual_gemm_forward(xa, hi_s, lo_s, sh_s, sl_s, BS)
+                ref_ms = t(lambda: rk.fused_act_quant_dual_gemm_forward(xa, hi_s, lo_s, sh_s, sl_s, BS), n=3, warm=1)
+                own_ms = t(lambda: fused_act_quant_dual_gemm_forward(xa, hi_s, lo_s, sh_s, sl_s, BS), n=5, warm=2)
+                small[f"N{n_out}"] = {"reference_fused_triton_ms": ref_ms, "ours_quantize_plus_gemm_ms": own_ms,
+                                      "speedup": ref_ms / own_ms}
+            out["act_quant_fused_small_n_M32768_K4096_bs64"] = small
+            del xa
         if ours_ms is not None:
             out["ours_block_scaled_dual_gemm_bs64"] = entry(ours_ms)
             ref = out.get("triton_block_scaled_dual_gemm_bs64")

@@ -484,8 +484,40 @@ EncodeTiledFn get_encode2() {
   return fn;
 }
 
+// A tensor map is a pure function of (address, shape, box, type, swizzle).  A
+// training step launches the same GEMMs on the same buffers over and over (the
+// caching allocator hands back the same addresses), so the encoded maps are
+// kept in a small per-thread direct-mapped table instead of being re-encoded
+// by the driver on every launch (seven per launch).
+struct MapKey {
+  const void* ptr;
+  int64_t rows, cols;
+  int32_t box_cols, box_rows, dt, swz, elem_bytes;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && box_cols == o.box_cols && box_rows == o.box_rows &&
+           dt == o.dt && swz == o.swz && elem_bytes == o.elem_bytes;
+  }
+};
+struct MapSlot {
+  MapKey key;
+  CUtensorMap map;
+  bool valid;
+};
+constexpr int kMapSlots = 512;
+
 int make_map2(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const void* ptr, int64_t rows, int64_t cols,
               int box_cols, int box_rows, CUtensorMapSwizzle swz) {
+  static thread_local MapSlot table[kMapSlots] = {};
+  const MapKey key{ptr, rows, cols, box_cols, box_rows, (int32_t)dt, (int32_t)swz, elem_bytes};
+  uint64_t h = reinterpret_cast<uintptr_t>(ptr) >> 4;
+  h ^= (uint64_t)rows * 0x9E3779B97F4A7C15ull ^ (uint64_t)cols * 0xC2B2AE3D27D4EB4Full ^ (uint64_t)(box_rows * 131 + box_cols) ^
+       ((uint64_t)dt << 40) ^ ((uint64_t)swz << 48);
+  h ^= h >> 29;
+  MapSlot& slot = table[h % kMapSlots];
+  if (slot.valid && slot.key == key) {
+    *map = slot.map;
+    return TCFP_OK;
+  }
   EncodeTiledFn enc = get_encode2();
   if (!enc) return fail(TCFP_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
   if ((reinterpret_cast<uintptr_t>(ptr) & 15u) || ((cols * elem_bytes) & 15))
@@ -497,6 +529,9 @@ int make_map2(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const vo
   CUresult r = enc(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(TCFP_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  slot.key = key;
+  slot.map = *map;
+  slot.valid = true;
   return TCFP_OK;
 }
 

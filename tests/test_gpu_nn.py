@@ -418,3 +418,95 @@ def test_quantized_weight_is_reused_between_optimizer_steps(kw):
         plain.weight.mul_(1.5)
     assert torch.equal(cached(xs[0]).detach(), plain(xs[0]).detach())
     assert K.is_triton_available()
+
+
+@pytest.mark.parametrize("kw", [dict(scale_block_size=64), dict()], ids=["block64", "per_tensor"])
+def test_layer_hooks_chunk_the_forward_and_see_the_input_gradient_first(kw):
+    """The hooks the tensor-parallel wrappers install: the forward output is
+    produced in row chunks on 128-row boundaries, each handed to ``out_hook``
+    as soon as its GEMM is queued (an in-place reduction there is part of the
+    layer's result), and ``dx_hook`` gets the input gradient before the weight
+    gradient is computed.  Chunked and unchunked layers agree bit for bit."""
+    from tcfp_b200.nn import LayerHooks, TCFPLinear
+
+    torch.manual_seed(11)
+    plain = TCFPLinear(256, 384, bias=False, use_tensor_cores=True, **kw).to(DEV)
+    hooked = TCFPLinear(256, 384, bias=False, use_tensor_cores=True, **kw).to(DEV)
+    hooked.load_state_dict(plain.state_dict())
+    seen = {"out": [], "dx": []}
+
+    class Handle:
+        def __init__(self):
+            self.waited = False
+
+        def wait(self):
+            self.waited = True
+
+    handles = []
+
+    def out_hook(chunk):
+        seen["out"].append((chunk.data_ptr(), tuple(chunk.shape)))
+        chunk.mul_(2.0)                      # stands in for an in-place all-reduce over two equal ranks
+        handles.append(Handle())
+        return handles[-1]
+
+    def dx_hook(g):
+        seen["dx"].append(tuple(g.shape))
+        g.mul_(2.0)
+        handles.append(Handle())
+        return handles[-1]
+
+    hooked._hooks = LayerHooks(out_hook=out_hook, row_chunks=4, dx_hook=dx_hook)
+    x1 = acts(95, 1000, 256).to(DEV).requires_grad_(True)
+    x2 = x1.detach().clone().requires_grad_(True)
+    y_ref = plain(x1)
+    y = hooked(x2)
+    assert torch.equal(y, 2.0 * y_ref)
+    assert [s for _, s in seen["out"]] == [(256, 384)] * 3 + [(232, 384)]
+    base = y.data_ptr()
+    assert [p for p, _ in seen["out"]] == [base + 256 * i * 384 * 4 for i in range(4)]
+    g = acts(96, 1000, 384, torch.float32).to(DEV)
+    y_ref.backward(g)
+    y.backward(g)
+    assert seen["dx"] == [(1000, 256)] and all(h.waited for h in handles)
+    assert torch.equal(x2.grad, 2.0 * x1.grad) and torch.equal(hooked.weight.grad, plain.weight.grad)
+
+
+def test_error_feedback_snapshot_does_not_stop_training(tmp_path):
+    """An asynchronous snapshot holds the state as of the call even though the
+    next step overwrites the error buffer in place while the copy to the host
+    is still in flight; the file written from the background thread restores
+    that state."""
+    from tcfp_b200.checkpoint import load_ef_state, save_ef_state_async, snapshot_ef_state_async
+    from tcfp_b200.nn import TCFPLinear
+
+    torch.manual_seed(2)
+    model = torch.nn.Sequential(TCFPLinear(512, 512, use_tensor_cores=True, scale_block_size=64),
+                                TCFPLinear(512, 256, use_tensor_cores=True)).to(DEV)
+    model[0]._param_name, model[1]._param_name = "a", "b"
+    opt = torch.optim.SGD(model.parameters(), lr=0.1)
+    x = acts(97, 256, 512).to(DEV)
+
+    def step():
+        opt.zero_grad()
+        model(x).square().mean().backward()
+        opt.step()
+
+    step()
+    want = {n: model[i]._error_state._buffers[n].clone() for i, n in ((0, "a"), (1, "b"))}
+    pending = snapshot_ef_state_async(model)
+    writer = save_ef_state_async(model, tmp_path / "ef_state.pt")
+    step()                                              # rewrites both buffers in place
+    assert not torch.equal(model[0]._error_state._buffers["a"], want["a"])
+    snap = pending.wait()
+    assert pending.done()
+    for n in ("a", "b"):
+        got = snap[n]["_buffers"][n]
+        assert got.device.type == "cpu" and got.is_pinned() and torch.equal(got, want[n].cpu())
+    writer.join(timeout=60)
+    fresh = torch.nn.Sequential(TCFPLinear(512, 512, use_tensor_cores=True, scale_block_size=64),
+                                TCFPLinear(512, 256, use_tensor_cores=True)).to(DEV)
+    fresh[0]._param_name, fresh[1]._param_name = "a", "b"
+    load_ef_state(fresh, tmp_path / "ef_state.pt")
+    for i, n in ((0, "a"), (1, "b")):
+        assert torch.equal(fresh[i]._error_state._buffers[n], want[n])

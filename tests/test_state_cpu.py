@@ -221,3 +221,41 @@ def test_convert_to_tcfp_signature_and_traversal_match_the_reference():
             assert ref_sig.parameters[n].kind == sig.parameters[n].kind
     finally:
         ref_loader.unload()
+
+
+def test_reference_checkpointer_loads_a_file_written_here(tmp_path):
+    """The other direction of the schema check: ``ef_state.pt`` written by
+    ``save_ef_state`` is restored by the reference's own
+    ``TCFPCheckpointer._load_ef_state`` (tcfp/training/checkpointing.py:225-271)
+    into the reference's own layers.  Needs ``oracle/_ref``; skips without it."""
+    import pytest
+
+    from oracle import ref_loader
+
+    if not ref_loader.available():
+        pytest.skip("oracle/_ref not built")
+    model = torch.nn.Sequential(torch.nn.Linear(32, 64), torch.nn.ReLU(), torch.nn.Linear(64, 32))
+    convert_to_tcfp(model, skip_patterns=(), use_tensor_cores=True, delayed_scaling=True)
+    for i, name in ((0, "0"), (2, "2")):
+        st = model[i]._error_state
+        st._buffers[name] = torch.randn(model[i].weight.shape)
+        st._amax_ema[name] = torch.tensor(0.5 + i)
+        st._delayed_amax[name + ".w_hi"] = torch.tensor(0.3 + i)
+        st._residual_ratio[name + ".ratio"] = torch.tensor(0.11 + i)
+        st._step_count[name + ".steps"] = 7 + i
+    save_ef_state(model, tmp_path / "ef_state.pt")
+    ref = ref_loader.load_reference()
+    try:
+        from tcfp.training.checkpointing import TCFPCheckpointer
+
+        theirs = torch.nn.Sequential(torch.nn.Linear(32, 64), torch.nn.ReLU(), torch.nn.Linear(64, 32))
+        ref.nn.convert_to_tcfp(theirs, skip_patterns=(), use_tensor_cores=True, delayed_scaling=True)
+        TCFPCheckpointer(tmp_path / "ckpts")._load_ef_state(tmp_path, theirs)
+        for i, name in ((0, "0"), (2, "2")):
+            a, b = model[i]._error_state, theirs[i]._error_state
+            for table in ("_buffers", "_amax_ema", "_delayed_amax", "_residual_ratio"):
+                da, db = getattr(a, table), getattr(b, table)
+                assert da.keys() == db.keys() and all(torch.equal(da[k], db[k]) for k in da)
+            assert a._step_count == b._step_count and a._ema_decay == b._ema_decay
+    finally:
+        ref_loader.unload()

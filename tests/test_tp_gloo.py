@@ -78,6 +78,23 @@ def _worker(rank: int, world: int, port: int, ret):
         ok &= torch.allclose(sp.up.inner.weight.grad, ref_up.weight.grad[s:e], atol=1e-5)
         ok &= torch.allclose(sp.down.inner.weight.grad, ref_down.weight.grad[:, s:e], atol=1e-5)
         ok &= torch.allclose(sp.down.bias.grad, ref_down.bias.grad, atol=1e-5)
+        # fused column-parallel group: one layer whose local weight is this rank's shard of each part
+        from tcfp_b200.tp import ColumnParallelLinear
+
+        ref_a, ref_b = torch.nn.Linear(d, 64), torch.nn.Linear(d, 96)
+        fused = ColumnParallelLinear(d, (64, 96), granule=granule, layer_factory=factory)
+        (a0, a1), (b0, b1) = fused.bounds
+        with torch.no_grad():
+            fused.inner.weight.copy_(torch.cat([ref_a.weight[a0:a1], ref_b.weight[b0:b1]]))
+            fused.inner.bias.copy_(torch.cat([ref_a.bias[a0:a1], ref_b.bias[b0:b1]]))
+        xf = x.clone().requires_grad_(True)
+        ya, yb = fused(xf)
+        (ya.square().sum() + yb.sum()).backward()
+        xg = x.clone().requires_grad_(True)
+        (ref_a(xg).square().sum() + ref_b(xg).sum()).backward()
+        ok &= ya.shape == (8, a1 - a0) and torch.allclose(ya, ref_a(x)[:, a0:a1], atol=1e-5)
+        ok &= torch.allclose(yb, ref_b(x)[:, b0:b1], atol=1e-5)
+        ok &= torch.allclose(xf.grad, xg.grad, atol=1e-4)                       # one all-reduce for the whole group
         # a token count the world size does not divide is refused, not truncated
         try:
             sp.down(torch.randn(3, e - s))
