@@ -57,18 +57,18 @@ __device__ __forceinline__ uint32_t pack4(uint8_t a, uint8_t b, uint8_t c, uint8
   return (uint32_t)a | ((uint32_t)b << 8) | ((uint32_t)c << 16) | ((uint32_t)d << 24);
 }
 
-// max of a non-negative value over aligned groups of GROUP lanes: non-negative
-// floats order like their bit patterns, so one integer warp-reduce per group
-// replaces a shuffle tree (every lane of the warp takes part, each with its
-// own group's member mask)
+// max of a non-negative value over aligned groups of GROUP lanes.  A whole
+// warp uses one integer warp-reduce (non-negative floats order like their bit
+// patterns); for smaller groups the reduce instruction's throughput loses to
+// a shuffle tree (measured: block 32 with 8-lane groups 170 vs 153 us at 8192^2).
 template <int GROUP>
 __device__ __forceinline__ float group_max(float v) {
   if constexpr (GROUP == 32) {
     return __uint_as_float(__reduce_max_sync(0xFFFFFFFFu, __float_as_uint(v)));
   } else {
-    const unsigned lane = threadIdx.x & 31u;
-    const unsigned mask = ((1u << GROUP) - 1u) << (lane & ~(unsigned)(GROUP - 1));
-    return __uint_as_float(__reduce_max_sync(mask, __float_as_uint(v)));
+#pragma unroll
+    for (int o = GROUP / 2; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+    return v;
   }
 }
 

@@ -426,7 +426,9 @@ def test_layer_hooks_chunk_the_forward_and_see_the_input_gradient_first(kw):
     produced in row chunks on 128-row boundaries, each handed to ``out_hook``
     as soon as its GEMM is queued (an in-place reduction there is part of the
     layer's result), and ``dx_hook`` gets the input gradient before the weight
-    gradient is computed.  Chunked and unchunked layers agree bit for bit."""
+    gradient is computed.  Chunked and unchunked layers agree to rounding (a
+    chunk of fewer than 256 rows runs on the one-SM kernel, whose accumulation
+    order differs from the pair kernel's)."""
     from tcfp_b200.nn import LayerHooks, TCFPLinear
 
     torch.manual_seed(11)
@@ -461,7 +463,8 @@ def test_layer_hooks_chunk_the_forward_and_see_the_input_gradient_first(kw):
     x2 = x1.detach().clone().requires_grad_(True)
     y_ref = plain(x1)
     y = hooked(x2)
-    assert torch.equal(y, 2.0 * y_ref)
+    torch.testing.assert_close(y, 2.0 * y_ref, rtol=1e-5, atol=1e-5)
+    assert torch.equal(y[:768], 2.0 * y_ref[:768])      # chunks of 256 rows: same kernel, same bits
     assert [s for _, s in seen["out"]] == [(256, 384)] * 3 + [(232, 384)]
     base = y.data_ptr()
     assert [p for p, _ in seen["out"]] == [base + 256 * i * 384 * 4 for i in range(4)]
