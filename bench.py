@@ -281,7 +281,7 @@ def _build_train_workload(name: str, dev, world: int, sp: bool):
         flop = 2.0 * tokens * d * h * 2 * 5           # two layers x (2 fwd + 2 dX + 1 dW) products
     elif name == "mlp_large":
         d, h, tokens, seed = 4096, 16384, 16 * 2048, 1004
-        model = build_mlp(d, h, srr=True).to(dev)
+        model = build_mlp(d, h, srr=True, reduce_dtype=torch.bfloat16).to(dev)     # bf16 partial sums on the wire
         opt_cls, lr = torch.optim.AdamW, 3e-4
         shape = (tokens, d)
         flop = 2.0 * tokens * d * h * 2 * 5
@@ -623,6 +623,12 @@ def run_ours(args) -> None:
                 extra[key] = _train_step_extra(name, dev, world, timed, steps)
             except Exception as e:
                 extra[key] = {"error": repr(e)[:200]}
+            torch.cuda.empty_cache()
+        if world > 1:
+            try:
+                extra["decoder_train_step_sequence_parallel"] = _train_step_extra("decoder", dev, world, timed, 3, sp=True)
+            except Exception as e:
+                extra["decoder_train_step_sequence_parallel"] = {"error": repr(e)[:200]}
             torch.cuda.empty_cache()
     line["extra"] = extra
     _C.check_device_status()

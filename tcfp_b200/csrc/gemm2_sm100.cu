@@ -40,7 +40,7 @@ constexpr int kBTile = 16384;         // per CTA: its half of the B operand(s)
 constexpr int kStageBytes = kATile + kBTile;
 constexpr int kSfStage = 3 * 512;
 constexpr int kPieceBytes = 16384;    // 128 rows x 128 B of staged output
-constexpr int kGroupM = 8;            // in units of 256-row tile rows
+constexpr int kGroupM = 8;            // default rasterisation group, in units of 256-row tile rows
 
 struct Gemm2Params {
   int M, N, K;
@@ -48,6 +48,7 @@ struct Gemm2Params {
   int has_lo;
   int a_fmt;
   int block_size;
+  int group_m;
   const float* s_a;
   const float* s_hi;
   const float* s_lo;
@@ -139,11 +140,11 @@ __host__ __device__ constexpr int smem_bytes2() {
 }
 
 // tile id -> (256-row block, column block); M fastest inside groups of kGroupM
-__device__ __forceinline__ void tile_coords2(int tile, int tiles_m, int tiles_n, int& mb, int& nb) {
-  const int per_group = kGroupM * tiles_n;
+__device__ __forceinline__ void tile_coords2(int tile, int tiles_m, int tiles_n, int group_m, int& mb, int& nb) {
+  const int per_group = group_m * tiles_n;
   const int group = tile / per_group;
-  const int first_m = group * kGroupM;
-  const int gm = min(tiles_m - first_m, kGroupM);
+  const int first_m = group * group_m;
+  const int gm = min(tiles_m - first_m, group_m);
   const int in_group = tile - group * per_group;
   mb = first_m + in_group % gm;
   nb = in_group / gm;
@@ -227,7 +228,7 @@ dual_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
       bool live = true;
       for (int tile = pair; live && tile < num_tiles; tile += num_pairs) {
         int mb, nb;
-        tile_coords2(tile, tiles_m, tiles_n, mb, nb);
+        tile_coords2(tile, tiles_m, tiles_n, p.group_m, mb, nb);
         const int row0 = mb * 2 * BM + (int)rank * BM;
         for (int ks = 0; ks < p.k_stages; ++ks) {
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status)) { live = false; break; }
@@ -372,7 +373,7 @@ dual_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
     bool live = true;
     for (int tile = pair; live && tile < num_tiles; tile += num_pairs) {
       int mb, nb;
-      tile_coords2(tile, tiles_m, tiles_n, mb, nb);
+      tile_coords2(tile, tiles_m, tiles_n, p.group_m, mb, nb);
       const int row0 = mb * 2 * BM + (int)rank * BM;
       if (!mbar_wait(bar_tfull + 8 * buf, buf_phase, abort_flag, p.status)) { live = false; break; }
       tc_fence_after();
@@ -571,6 +572,10 @@ int launch2(const void* a, const void* b_hi, const void* b_lo, const void* sf_a,
   }
 
   p.status = device_status_ptr();
+  // rows of tiles swept together before moving to the next column band: a larger group re-reads the B
+  // operand from HBM fewer times (8192^3: 16 instead of 8 cut the per-tensor forward from 0.740 to 0.720 ms
+  // and its dX from 0.724 to 0.702 ms; the block-scaled kind measured no better, 32 measured worse for all)
+  p.group_m = (KIND == KIND_F8) ? 2 * kGroupM : kGroupM;
   p.k_stages = (p.K + T::kStageK - 1) / T::kStageK;
   p.has_lo = b_lo != nullptr;
   constexpr int smem = smem_bytes2<KIND>();

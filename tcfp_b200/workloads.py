@@ -42,7 +42,7 @@ class DecoderLayer(nn.Module):
     reduce-scatter after each row-parallel layer (same bytes on the wire)."""
 
     def __init__(self, d_model: int, n_heads: int, ffn: int, *, granule: int = 64, sequence_parallel: bool = False,
-                 overlap_chunks: int = 4, **layer_kw):
+                 overlap_chunks: int = 1, **layer_kw):
         super().__init__()
         world = _world()
         assert n_heads % world == 0, "heads must divide over the tensor-parallel ranks"
@@ -105,7 +105,7 @@ class Decoder(nn.Module):
 
 
 def build_decoder(n_layers=4, d_model=4096, n_heads=32, ffn=11008, block=64, *, sequence_parallel=False,
-                  overlap_chunks=4, **layer_kw) -> nn.Module:
+                  overlap_chunks=1, **layer_kw) -> nn.Module:
     kw = dict(scale_block_size=block, out_dtype=torch.bfloat16, **layer_kw)
     m = Decoder([DecoderLayer(d_model, n_heads, ffn, granule=block, sequence_parallel=sequence_parallel,
                               overlap_chunks=overlap_chunks, **kw) for _ in range(n_layers)])
