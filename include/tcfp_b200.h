@@ -63,6 +63,16 @@ typedef enum {
 int32_t tcfp_version(void);
 /* copies the calling thread's last error text (NUL-terminated) into buf */
 int32_t tcfp_last_error(char* buf, size_t n);
+/*
+ * No counterpart in the reference.  The GEMM kernels are persistent: one CTA
+ * (pair) per SM for the whole launch, so a collective's kernel queued beside
+ * one finds no SM to run on until the GEMM ends.  tcfp_set_sm_reserve(n) makes
+ * the GEMM entry points called afterwards FROM THE SAME HOST THREAD size their
+ * grids for (SM count - n) SMs, leaving n for the collective; 0 restores the
+ * full grid.  Returns the previous value (>= 0), or TCFP_ERR_INVALID.
+ */
+int32_t tcfp_set_sm_reserve(int32_t n);
+
 /* Synchronises ``stream`` and returns TCFP_ERR_DEVICE if any kernel of this
  * library recorded a timed-out wait since the last call (and clears the
  * record).  The hot path never calls this; tests and debug builds do. */

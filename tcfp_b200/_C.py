@@ -22,6 +22,7 @@ Q_NONE, Q_EF, Q_EF_READONLY, Q_SRR = 0, 1, 2, 3
 _SIGNATURES = {
     "tcfp_version": (c_int32, []),
     "tcfp_last_error": (c_int32, [c_char_p, c_size_t]),
+    "tcfp_set_sm_reserve": (c_int32, [c_int32]),
     "tcfp_check_device_status": (c_int32, [c_void_p]),
     "tcfp_selftest_bounded_wait": (c_int32, [c_uint64, c_void_p]),
     "tcfp_dual_quantize": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -108,6 +109,23 @@ def ptr(t: torch.Tensor | None):
 
 def stream():
     return torch.cuda.current_stream().cuda_stream
+
+
+class sm_reserve:
+    """Context manager: the GEMMs launched inside leave ``n`` SMs free (for a
+    collective running beside them); see ``tcfp_set_sm_reserve``."""
+
+    def __init__(self, n: int):
+        self.n = int(n)
+
+    def __enter__(self):
+        self.prev = load().tcfp_set_sm_reserve(self.n) if self.n > 0 else None
+        return self
+
+    def __exit__(self, *exc):
+        if self.prev is not None:
+            load().tcfp_set_sm_reserve(max(self.prev, 0))
+        return False
 
 
 def dtype_code(t: torch.Tensor) -> int:

@@ -29,9 +29,23 @@ int sm_count() {
   return cached[dev];
 }
 
+static thread_local int t_sm_reserve = 0;
+
+int gemm_sm_budget() {
+  const int n = sm_count() - t_sm_reserve;
+  return n < 2 ? 2 : n;
+}
+
 }  // namespace tcfp
 
 extern "C" int32_t tcfp_version(void) { return 100; }
+
+extern "C" int32_t tcfp_set_sm_reserve(int32_t n) {
+  if (n < 0 || n > 128) return tcfp::fail(TCFP_ERR_INVALID, "sm_reserve must be in [0, 128], got %d", n);
+  const int prev = tcfp::t_sm_reserve;
+  tcfp::t_sm_reserve = n;
+  return prev;
+}
 
 extern "C" int32_t tcfp_last_error(char* buf, size_t n) {
   if (!buf || n == 0) return TCFP_ERR_INVALID;

@@ -590,7 +590,7 @@ int launch2(const void* a, const void* b_hi, const void* b_lo, const void* sf_a,
   }
   const int tile_n = (!T::kSum && !p.has_lo) ? 2 * BN : BN;
   const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + tile_n - 1) / tile_n);
-  const int max_pairs = sm_count() / 2;
+  const int max_pairs = gemm_sm_budget() / 2;
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);

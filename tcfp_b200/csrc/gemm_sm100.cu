@@ -469,7 +469,7 @@ int launch(const void* a, const void* b_hi, const void* b_lo, void* out, GemmPar
     configured[dev] = true;
   }
   const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
-  const int grid = tiles < sm_count() ? tiles : sm_count();
+  const int grid = tiles < gemm_sm_budget() ? tiles : gemm_sm_budget();
   kern<<<grid, kThreads, smem, stream>>>(tm_a, tm_bhi, tm_blo, tm_out, p);
   CUDA_TRY(cudaGetLastError());
   return TCFP_OK;

@@ -14,6 +14,9 @@ namespace tcfp {
 int fail(int code, const char* fmt, ...);
 // number of SMs of the current device (cached per device)
 int sm_count();
+// SMs the persistent GEMM grids may occupy: sm_count() minus the calling thread's
+// tcfp_set_sm_reserve() (SMs left free for a collective running beside the GEMM)
+int gemm_sm_budget();
 
 }  // namespace tcfp
 

@@ -72,10 +72,13 @@ class LayerHooks:
     return ``None`` or an object whose ``wait()`` makes the current stream
     wait for the collective."""
 
-    def __init__(self, out_hook=None, row_chunks: int = 1, dx_hook=None):
+    def __init__(self, out_hook=None, row_chunks: int = 1, dx_hook=None, reserve_sms: int = 0):
         self.out_hook = out_hook
         self.row_chunks = max(1, int(row_chunks))
         self.dx_hook = dx_hook
+        # SMs the weight-gradient GEMM leaves free while the collective started by dx_hook is in flight
+        # (the GEMMs are persistent, one CTA per SM: without free SMs the collective's kernel cannot start)
+        self.reserve_sms = int(reserve_sms)
 
 
 def _row_chunks(M: int, hooks) -> list[tuple[int, int]]:
@@ -184,6 +187,7 @@ class _TCFP12TensorCoreFunction(torch.autograd.Function):
                 pending.append(hooks.out_hook(out2d[r0:r1]))
         _wait_all(pending)
         ctx.dx_hook = None if hooks is None else hooks.dx_hook
+        ctx.reserve_sms = 0 if hooks is None else hooks.reserve_sms
         ctx.dx_dtype = _dx_dtype(input)
         ctx.hp_grad_weight = hp_grad_weight
         ctx.input_shape = input_shape
@@ -219,13 +223,14 @@ class _TCFP12TensorCoreFunction(torch.autograd.Function):
                                                  out_dtype=ctx.dx_dtype)
         dx_pending = ctx.dx_hook(grad_input) if ctx.dx_hook is not None else None   # overlaps the dW GEMM below
         grad_input = grad_input.reshape(ctx.input_shape)
-        if ctx.hp_grad_weight:
-            if saved_act.dtype == torch.bfloat16 and g2d.shape[1] % 16 == 0 and saved_act.shape[1] % 16 == 0:
-                grad_weight = bf16_weight_grad(g2d, saved_act)
+        with _C.sm_reserve(ctx.reserve_sms if dx_pending is not None else 0):
+            if ctx.hp_grad_weight:
+                if saved_act.dtype == torch.bfloat16 and g2d.shape[1] % 16 == 0 and saved_act.shape[1] % 16 == 0:
+                    grad_weight = bf16_weight_grad(g2d, saved_act)
+                else:
+                    grad_weight = g2d.float().t() @ saved_act.float()    # (:541-542)
             else:
-                grad_weight = g2d.float().t() @ saved_act.float()    # (:541-542)
-        else:
-            grad_weight = fp8_weight_grad(grad_fp8, saved_act, grad_inv, act_inv)   # (:546-555)
+                grad_weight = fp8_weight_grad(grad_fp8, saved_act, grad_inv, act_inv)   # (:546-555)
         _wait_all([dx_pending])
         return (grad_input, grad_weight, grad_bias) + (None,) * 13
 
@@ -270,6 +275,7 @@ class _TCFP12BlockScaledFunction(torch.autograd.Function):
                 pending.append(hooks.out_hook(out2d[r0:r1]))
         _wait_all(pending)
         ctx.dx_hook = None if hooks is None else hooks.dx_hook
+        ctx.reserve_sms = 0 if hooks is None else hooks.reserve_sms
         ctx.dx_dtype = _dx_dtype(input)
         ctx.hp_grad_weight = hp_grad_weight
         ctx.input_shape = input_shape
@@ -312,14 +318,15 @@ class _TCFP12BlockScaledFunction(torch.autograd.Function):
         dx_pending = ctx.dx_hook(grad_input) if ctx.dx_hook is not None else None   # overlaps the dW GEMM below
         grad_input = grad_input.reshape(ctx.input_shape)
         # dW in full precision, as in the reference (:744-750)
-        if ctx.hp_grad_weight:
-            if saved_act.dtype == torch.bfloat16:
-                grad_weight = bf16_weight_grad(g2d, saved_act)
+        with _C.sm_reserve(ctx.reserve_sms if dx_pending is not None else 0):
+            if ctx.hp_grad_weight:
+                if saved_act.dtype == torch.bfloat16:
+                    grad_weight = bf16_weight_grad(g2d, saved_act)
+                else:
+                    grad_weight = g2d.float().t() @ saved_act.float()
             else:
-                grad_weight = g2d.float().t() @ saved_act.float()
-        else:
-            # the saved codes dequantize exactly to bf16; the FP32 gradient goes in as bf16 head + tail
-            grad_weight = bf16_weight_grad(g2d, block_dequantize_bf16(saved_act, act_scales, bs))
+                # the saved codes dequantize exactly to bf16; the FP32 gradient goes in as bf16 head + tail
+                grad_weight = bf16_weight_grad(g2d, block_dequantize_bf16(saved_act, act_scales, bs))
         _wait_all([dx_pending])
         return (grad_input, grad_weight, grad_bias) + (None,) * 12
 

@@ -237,7 +237,7 @@ class ColumnParallelLinear(nn.Module):
 
     def __init__(self, in_features: int, out_features, bias: bool = True, *, group=None, granule: int = 16,
                  layer_factory: Callable[..., nn.Module] = _default_factory, reduce_input_grad: bool = True,
-                 **layer_kw):
+                 comm_sms: int = 32, **layer_kw):
         super().__init__()
         self.group = group
         # several column-parallel layers fed by one tensor may share a single gradient all-reduce:
@@ -257,7 +257,8 @@ class ColumnParallelLinear(nn.Module):
         if self._overlap:
             from .nn import LayerHooks
 
-            self.inner._hooks = LayerHooks(dx_hook=lambda g: _all_reduce_async(g, self.group))
+            # the weight-gradient GEMM leaves `comm_sms` SMs to NCCL while the input gradient is being reduced
+            self.inner._hooks = LayerHooks(dx_hook=lambda g: _all_reduce_async(g, self.group), reserve_sms=comm_sms)
 
     def forward(self, x: torch.Tensor):
         if self.reduce_input_grad and not self._overlap:

@@ -258,3 +258,27 @@ def test_block_backward_dx_routes_agree_and_reuse_the_retargeted_weight(bs):
     hi_only = fused_block_scaled_backward_dx(d(gq), dhi, None, d(eg), deh, None, bs, out_dtype=torch.bfloat16)
     assert hi_only.dtype == torch.bfloat16
     assert rel_fro(hi_only.float(), O.block_backward_dx(gq, eg, hi, eh, None, None, bs)) <= 5e-3
+
+
+def test_sm_reserve_shrinks_the_grid_not_the_result(lib):
+    """GEMMs launched while SMs are reserved (for a collective beside them)
+    walk the same tiles with fewer CTAs: identical bits; the setting is
+    per host thread, validated, and restored by the context manager."""
+    from tcfp_b200 import _C
+    from tcfp_b200.kernels import fused_block_scaled_dual_gemm_forward, fused_dual_gemm_forward
+
+    a, ea, hi, eh, lo, el = _block_operands(305, 1024, 768, 512, 64)
+    d = lambda t: t.to(DEV)  # noqa: E731
+    ops = [d(t) for t in (a, hi, lo, ea, eh, el)]
+    full = fused_block_scaled_dual_gemm_forward(*ops, 64)
+    with _C.sm_reserve(32):
+        assert lib.tcfp_set_sm_reserve(32) == 32          # reads back what the context manager set
+        part = fused_block_scaled_dual_gemm_forward(*ops, 64)
+    assert lib.tcfp_set_sm_reserve(0) == 0                # restored on exit
+    assert torch.equal(part, full)
+    pa, ia, phi, ihi, plo, ilo = [d(t) for t in _per_tensor_operands(306, 200, 256, 384)]   # small M: one-SM kernel
+    full = fused_dual_gemm_forward(pa, phi, plo, ia, ihi, ilo)
+    with _C.sm_reserve(100):
+        assert torch.equal(fused_dual_gemm_forward(pa, phi, plo, ia, ihi, ilo), full)
+    assert lib.tcfp_set_sm_reserve(-1) == -1 and "sm_reserve" in _C.last_error()
+    assert lib.tcfp_set_sm_reserve(500) == -1
