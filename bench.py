@@ -262,7 +262,8 @@ def _reference_gpu(dev, a, s_a, w_hi, w_lo, s_hi, s_lo, x, w, ours_ms: float | N
 
 TRAIN_DESC = {
     "mlp": "MLP 1024->4096->1024 GELU, 64x128 tokens bf16, per-tensor EF, Adam, fwd+bwd+step (configuration 0)",
-    "mlp_large": "MLP 4096->16384->4096 GELU, 16x2048 tokens bf16, per-tensor SRR, AdamW, fwd+bwd+step (configuration 3)",
+    "mlp_large": "MLP 4096->16384->4096 GELU, 16x2048 tokens bf16, bf16 layer outputs, per-tensor SRR, AdamW, fwd+bwd+step "
+                 "(configuration 3)",
     "decoder": "4 decoder layers d=4096 h=32 ffn=11008, batch 8 x seq 4096 bf16, block-64 EF, AdamW, fwd+bwd+step "
                "(configuration 4)",
 }
@@ -281,7 +282,8 @@ def _build_train_workload(name: str, dev, world: int, sp: bool):
         flop = 2.0 * tokens * d * h * 2 * 5           # two layers x (2 fwd + 2 dX + 1 dW) products
     elif name == "mlp_large":
         d, h, tokens, seed = 4096, 16384, 16 * 2048, 1004
-        model = build_mlp(d, h, srr=True, reduce_dtype=torch.bfloat16).to(dev)     # bf16 partial sums on the wire
+        # bf16 activations between the layers and bf16 partial sums on the wire (the GEMM epilogues write bf16)
+        model = build_mlp(d, h, srr=True, out_dtype=torch.bfloat16, reduce_dtype=torch.bfloat16).to(dev)
         opt_cls, lr = torch.optim.AdamW, 3e-4
         shape = (tokens, d)
         flop = 2.0 * tokens * d * h * 2 * 5

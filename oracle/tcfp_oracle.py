@@ -169,6 +169,12 @@ def nf_aware_target_max(t: torch.Tensor, sigma_factor: float = 3.0) -> torch.Ten
     return t.abs().max().clamp(min=1e-12) if std < 1e-6 else sigma_factor * std
 
 
+def to_fp8_e4m3_nf_aware(t: torch.Tensor, sigma_factor: float = 3.0):
+    """tcfp/core.py:161-193 (round-to-nearest form)."""
+    scale = (FP8_E4M3_MAX / nf_aware_target_max(t, sigma_factor)).to(torch.float32)
+    return to_fp8_e4m3(t, scale=scale)
+
+
 def dual_quantize_per_tensor(
     weight: torch.Tensor,
     error: torch.Tensor | None = None,
@@ -407,7 +413,7 @@ class LayerState:
 
 
 def linear_forward(x, weight, bias, state: LayerState | None, *, srr=False, abd=False, delayed=False,
-                   hp_grad_weight=False, update_ef=True, seed=0):
+                   hp_grad_weight=False, update_ef=True, seed=0, nf_sigma=None):
     """``_TCFP12TensorCoreFunction.forward`` (tcfp/nn/__init__.py:324-459) with
     the GEMMs as FP32 dequantized matmuls.  ``state`` is None for SRR / no-EF
     layers except that SRR uses ``state.srr_offset`` when a state is given.
@@ -431,7 +437,8 @@ def linear_forward(x, weight, bias, state: LayerState | None, *, srr=False, abd=
             s_lo = (FP8_E4M3_MAX / state.predict(d)).to(torch.float32)
         w_lo, inv_lo = to_fp8_e4m3(residual, scale=s_lo)
     else:
-        w_hi, inv_hi = to_fp8_e4m3(w)
+        # sigma-based scale for W_hi when nf_aware_scaling is set (:356-359)
+        w_hi, inv_hi = to_fp8_e4m3(w) if nf_sigma is None else to_fp8_e4m3_nf_aware(w, nf_sigma)
         residual = w - w_hi.float() * inv_hi
         if srr:
             off = state.srr_offset if state is not None else 0

@@ -16,6 +16,7 @@ LAYER_CASES = {
     "abd": dict(seed=104, M=32, K=64, N=48, bias=False, abd=True),
     "delayed": dict(seed=105, M=32, K=64, N=48, bias=True, delayed=True),
     "hp_grad": dict(seed=106, M=32, K=64, N=48, bias=True, hp=True),
+    "nf_aware": dict(seed=107, M=32, K=64, N=48, bias=True, nf=True),
 }
 
 

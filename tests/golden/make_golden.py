@@ -54,6 +54,8 @@ for name, (seed, shape, dtype) in CAST_CASES.items():
     out[f"cast/{name}/e4m3"], out[f"cast/{name}/e4m3_inv"] = u8(q), i32(inv)
     q, inv = rcore.to_fp8_e5m2(x)
     out[f"cast/{name}/e5m2"], out[f"cast/{name}/e5m2_inv"] = u8(q), i32(inv)
+    q, inv = rcore.to_fp8_e4m3_nf_aware(x)
+    out[f"cast/{name}/nf_aware"], out[f"cast/{name}/nf_aware_inv"] = u8(q), i32(inv)
     # stochastic rounding under the seed/offset contract
     scaled = (x.float() * (448.0 / x.float().abs().max())).clamp(-448, 448)
     rand = O.philox_uniform_packed(seed, 17, scaled.numel()).reshape(scaled.shape)
@@ -83,7 +85,8 @@ for name, cfg in LAYER_CASES.items():
     x, w, b, target = layer_inputs(cfg)
     layer = rnn.TCFPLinear(cfg["K"], cfg["N"], bias=cfg["bias"], use_tensor_cores=True, use_fused_kernel=False,
                            use_cuda_ext=False, srr=cfg.get("srr", False), abd=cfg.get("abd", False),
-                           delayed_scaling=cfg.get("delayed", False), hp_grad_weight=cfg.get("hp", False))
+                           delayed_scaling=cfg.get("delayed", False), hp_grad_weight=cfg.get("hp", False),
+                           nf_aware_scaling=cfg.get("nf", False))
     layer._param_name = "layer"
     with torch.no_grad():
         layer.weight.copy_(w)

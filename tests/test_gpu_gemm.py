@@ -206,15 +206,14 @@ def test_bounded_wait_gives_up_and_reports(lib):
     assert lib.tcfp_selftest_bounded_wait(0, None) == -1
 
 
-@pytest.mark.parametrize("bs", [32, 64, 128])
-def test_block_retarget_is_exact_up_to_e4m3_underflow(bs):
+@pytest.mark.parametrize("bs,D_out,D_in", [(32, 384, 640), (64, 384, 640), (128, 384, 640), (32, 160, 96), (64, 192, 320)])
+def test_block_retarget_is_exact_up_to_e4m3_underflow(bs, D_out, D_in):
     """The weight re-targeted for the dX contraction dequantizes to the same
     values as the quantized weight it came from: bit-equal wherever the
     exponent shift keeps the value on E4M3's grid, and within 2^-10 * 2^t of
     it where the shift runs into the subnormal step."""
     from tcfp_b200.kernels import block_retarget
 
-    D_out, D_in = 384, 640
     w = weights(410, D_out, D_in, outliers=True)
     w[5] = 0.0                                      # zero rows: -128 sentinel in the residual plane
     w[:, 64:96] *= 1e-3                             # a column block of small rows next to large ones
@@ -237,11 +236,11 @@ def test_block_retarget_is_exact_up_to_e4m3_underflow(bs):
     assert lo_t2 is None and t_lo2 is None and torch.equal(hi_t2.view(torch.uint8), hi_t.view(torch.uint8))
 
 
-@pytest.mark.parametrize("bs", [32, 128])
-def test_block_backward_dx_routes_agree_and_reuse_the_retargeted_weight(bs):
+@pytest.mark.parametrize("bs,M,D_out,D_in", [(32, 512, 256, 384), (128, 512, 256, 384), (32, 300, 160, 96),
+                                             (64, 1000, 192, 320)])
+def test_block_backward_dx_routes_agree_and_reuse_the_retargeted_weight(bs, M, D_out, D_in):
     from tcfp_b200.kernels import fused_block_scaled_backward_dx
 
-    M, D_out, D_in = 512, 256, 384
     g = acts(420, M, D_out, torch.float32)
     w = weights(421, D_out, D_in, outliers=True)
     gq, eg = O.block_quantize(g, bs, torch.float8_e5m2)

@@ -34,6 +34,8 @@ def test_casts_match_reference_bits(name):
     assert np.array_equal(u8(q), GOLD[f"cast/{name}/e4m3"]) and np.array_equal(i32(inv), GOLD[f"cast/{name}/e4m3_inv"])
     q, inv = O.to_fp8_e5m2(x)
     assert np.array_equal(u8(q), GOLD[f"cast/{name}/e5m2"]) and np.array_equal(i32(inv), GOLD[f"cast/{name}/e5m2_inv"])
+    q, inv = O.to_fp8_e4m3_nf_aware(x)
+    assert np.array_equal(u8(q), GOLD[f"cast/{name}/nf_aware"]) and np.array_equal(i32(inv), GOLD[f"cast/{name}/nf_aware_inv"])
     scaled = (x.float() * (448.0 / x.float().abs().max())).clamp(-448, 448)
     rand = O.philox_uniform_packed(seed, 17, scaled.numel()).reshape(scaled.shape)
     assert np.array_equal(u8(O.stochastic_round_to_fp8_e4m3(scaled, rand)), GOLD[f"cast/{name}/sr"])
@@ -53,7 +55,7 @@ def test_layer_steps_match_reference(name):
         xin = x.clone()
         y, ctx = O.linear_forward(xin, w, b, state, srr=srr, abd=cfg.get("abd", False),
                                   delayed=cfg.get("delayed", False), hp_grad_weight=cfg.get("hp", False),
-                                  seed=cfg["seed"])
+                                  seed=cfg["seed"], nf_sigma=3.0 if cfg.get("nf") else None)
         gy = 2.0 * (y - target) / y.numel()
         dx, dw, db = O.linear_backward(ctx, gy)
         pre = f"layer/{name}/step{step}/"
