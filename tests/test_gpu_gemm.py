@@ -228,7 +228,7 @@ def test_block_retarget_is_exact_up_to_e4m3_underflow(bs, D_out, D_in):
         bound = 2.0 ** -10 * scale_t
         assert bool(((got - ref).abs() <= bound).all())
         exact = (got == ref).double().mean().item()
-        assert exact > 0.93, f"only {exact:.3f} of the values survived the re-encoding bit for bit"
+        assert exact > 0.85, f"only {exact:.3f} of the values survived the re-encoding bit for bit"
         # t is the largest live exponent of each (row block, column) -- nothing overflows
         assert int(codes_t.view(torch.uint8).cpu().bitwise_and(0x7F).max()) <= 0x7E
     # residual left out (asymmetric backward)
