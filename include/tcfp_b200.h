@@ -231,6 +231,28 @@ int32_t tcfp_block_dual_gemm(const uint8_t* a, const uint8_t* sf_a,
                              int32_t block_size, void* stream);
 
 /*
+ * Block-scaled forward with the activation quantizer fused into the GEMM
+ * prologue: x (M,K) bf16 is block-quantized to E4M3 + E8M0 inside the K loop
+ * by converter warps (same bytes as tcfp_quantize(block_size) produces) and
+ * multiplied against W_hi / W_lo as in tcfp_block_dual_gemm.  act_codes_out
+ * (M,K) and act_exps_out (K/bs, M) int8 -- both or neither -- receive the
+ * quantized activation for the backward pass, written by the CTAs of the
+ * first column tile only.  Every column tile re-quantizes its A tiles, so
+ * this pays for narrow layers only.  Replaces
+ * fused_act_quant_dual_gemm_forward (tcfp/kernels.py:2031-2149, kernel
+ * :826-1041), which the reference dispatches for N <= 512
+ * (tcfp/nn/__init__.py:620-640).
+ */
+int32_t tcfp_block_dual_gemm_fused_act(const void* x_bf16, const uint8_t* w_hi,
+                                       const uint8_t* sf_hi, const uint8_t* w_lo,
+                                       const uint8_t* sf_lo, const float* bias,
+                                       void* out, int32_t out_dtype,
+                                       uint8_t* act_codes_out,
+                                       int8_t* act_exps_out, int64_t M,
+                                       int64_t N, int64_t K, int32_t block_size,
+                                       void* stream);
+
+/*
  * No counterpart in the reference.  Same result as tcfp_pack_scales (x3)
  * followed by tcfp_block_dual_gemm, for callers that hold the scales as
  * reference-layout int8 exponent planes (K/bs, rows) and cannot allocate the

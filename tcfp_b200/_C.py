@@ -46,6 +46,9 @@ _SIGNATURES = {
                                c_int64, c_void_p]),
     "tcfp_block_dual_gemm": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                        c_void_p, c_int32, c_int64, c_int64, c_int64, c_int32, c_void_p]),
+    "tcfp_block_dual_gemm_fused_act": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                 c_int32, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int32,
+                                                 c_void_p]),
     "tcfp_block_retarget": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                       c_int64, c_int64, c_int32, c_void_p]),
     "tcfp_block_dx_gemm": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32,

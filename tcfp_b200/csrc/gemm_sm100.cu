@@ -475,6 +475,365 @@ int launch(const void* a, const void* b_hi, const void* b_lo, void* out, GemmPar
   return TCFP_OK;
 }
 
+
+// ---------------------------------------------------------------------------
+// Activation quantization fused into the GEMM prologue (block-scaled kind).
+//
+// The reference's counterpart is _fused_act_quant_dual_gemm_kernel
+// (tcfp/kernels.py:826-1041): the bf16 activation tile is block-quantized
+// inside the K loop (:960-976) and the quantized activation is written out
+// from the first column tile only (:1011-1021).  Here, per CTA of 128 x 128
+// output:
+//   warp 0        TMA producer: W_hi / W_lo tiles and their scale chunks
+//   warp 1        MMA issuer (one 128 x 256 block-scaled MMA per 32 K)
+//   warps 2-5     epilogue
+//   warps 6-13    converters, two sets of four warps taking alternate K
+//                 stages: thread r of a set owns row r of the tile, reads its
+//                 128 bf16 values of the stage with 128-bit loads, finds each
+//                 scale block's amax in registers (no shuffles), writes the
+//                 E4M3 codes into the 128-byte-swizzled A stage and the E8M0
+//                 bytes into the stage's scale chunk, and -- in the CTAs of
+//                 column tile 0 -- the side outputs to global memory.
+// A stage is released to the MMA warp by the TMA transaction count (B) plus
+// one arrival per converter warp (A), after a generic->async proxy fence.
+// The A scale chunk is always written at 32-element granularity (a block of
+// 64 / 128 repeats its byte), so the MMA addresses A scales by j and B scales
+// by the weight's own block size.
+// ---------------------------------------------------------------------------
+constexpr int kFusedThreads = 192 + 256;
+
+template <int BS, bool OUT_BF16>
+__global__ void __launch_bounds__(kFusedThreads, 1)
+fused_act_dual_gemm_kernel(const __nv_bfloat16* __restrict__ x, const __grid_constant__ CUtensorMap tm_bhi,
+                           const __grid_constant__ CUtensorMap tm_blo, const __grid_constant__ CUtensorMap tm_out,
+                           uint8_t* __restrict__ act_out, int8_t* __restrict__ act_exps, const GemmParams p) {
+  constexpr int kAccCols = 2 * BN;
+  constexpr uint32_t kTmemCols = 512;
+  constexpr int kSfColBase = kAccCols;
+  constexpr int kBlocksPerStage = 128 / BS;       // scale blocks of the activation per K stage
+  constexpr int kVecPerBlock = BS / 8;            // 128-bit loads per scale block
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* stage_base = smem;
+  uint8_t* staging = stage_base + kStages * kStageBytes;
+  uint8_t* sf_base = staging + staging_bytes<OUT_BF16>();
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sf_base + kStages * kSfStageBytes);
+  const uint32_t bar_full = smem_u32(bars);
+  const uint32_t bar_empty = smem_u32(bars + kStages);
+  const uint32_t bar_tfull = smem_u32(bars + 2 * kStages);
+  const uint32_t bar_tempty = smem_u32(bars + 2 * kStages + 2);
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tiles_m = (p.M + BM - 1) / BM;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar_full + 8 * s, 1 + 4);     // producer's expect_tx arrival + four converter warps
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_tfull + 8 * b, 1);
+      mbar_init(bar_tempty + 8 * b, kEpiThreads);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0 && lane == 0) {
+    prefetch_tmap(&tm_bhi);
+    prefetch_tmap(&tm_blo);
+    prefetch_tmap(&tm_out);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_holder), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ======================= TMA producer: weights and their scales =======================
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      const uint32_t tx_bytes = (p.has_lo ? 2 : 1) * (kBHalfBytes + 512);
+      const int k_groups = ((p.K / BS) + 3) / 4;
+      bool live = true;
+      for (int tile = blockIdx.x; live && tile < num_tiles; tile += gridDim.x) {
+        int mb, nb;
+        tile_coords(tile, tiles_m, tiles_n, mb, nb);
+        for (int ks = 0; ks < p.k_stages; ++ks) {
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status)) { live = false; break; }
+          const uint32_t full = bar_full + 8 * stage;
+          mbar_expect_tx(full, tx_bytes);
+          const uint32_t sb = smem_u32(stage_base + stage * kStageBytes) + kATileBytes;
+          const int k0 = ks * 128;
+          tma_load_2d(sb, &tm_bhi, k0, nb * BN, full);
+          if (p.has_lo) tma_load_2d(sb + kBHalfBytes, &tm_blo, k0, nb * BN, full);
+          const int kg = (ks * 4) / (BS / 32) / 4;
+          const uint32_t ssf = smem_u32(sf_base + stage * kSfStageBytes);
+          bulk_load_1d(ssf + 512, p.sf_hi + ((size_t)nb * k_groups + kg) * 512, 512, full);
+          if (p.has_lo) bulk_load_1d(ssf + 1024, p.sf_lo + ((size_t)nb * k_groups + kg) * 512, 512, full);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ======================= MMA issuer =======================
+    if (elect_one()) {
+      const uint32_t n_mma = p.has_lo ? 2 * BN : BN;
+      const uint32_t idesc = ((uint32_t)TCFP_E4M3 << 7) | ((n_mma >> 3) << 17) | (1u << 23) | ((uint32_t)(BM >> 4) << 24);
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t buf_phase = 0;
+      bool live = true;
+      for (int tile = blockIdx.x; live && tile < num_tiles; tile += gridDim.x) {
+        if (!mbar_wait(bar_tempty, buf_phase ^ 1, abort_flag, p.status)) { live = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base;
+        for (int ks = 0; ks < p.k_stages; ++ks) {
+          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status)) { live = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(stage_base + stage * kStageBytes);
+          const uint32_t sb = sa + kATileBytes;
+          const uint32_t ssf = smem_u32(sf_base + stage * kSfStageBytes);
+          const uint32_t tsfa = tmem_base + (uint32_t)(kSfColBase + stage * 16);
+          const uint32_t tsfb = tsfa + 4;
+          tc_cp_sf(tsfa, make_desc(ssf, 0, 128, 0));
+          tc_cp_sf(tsfb, make_desc(ssf + 512, 0, 128, 0));
+          if (p.has_lo) tc_cp_sf(tsfb + 4, make_desc(ssf + 1024, 0, 128, 0));
+          int sf_first, sf_shift;
+          if (BS == 32) { sf_first = 0; sf_shift = 0; }
+          else if (BS == 64) { sf_first = 2 * (ks & 1); sf_shift = 1; }
+          else { sf_first = ks & 3; sf_shift = 2; }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint64_t adesc = make_desc(sa + j * 32u, 16u, 1024, 2);
+            const uint64_t bdesc = make_desc(sb + j * 32u, 16u, 1024, 2);
+            const uint32_t b_sfid = (uint32_t)(sf_first + (j >> sf_shift));
+            const uint32_t id = idesc | ((uint32_t)j << 29) | (b_sfid << 4);     // A scales per 32, B scales per BS
+            tc_mma<KIND_MXF8>(d_tmem, adesc, bdesc, id, (ks | j) != 0 ? 1u : 0u, tsfa, tsfb);
+          }
+          tc_commit(bar_empty + 8 * stage);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        if (!live) break;
+        tc_commit(bar_tfull);
+        buf_phase ^= 1;
+      }
+    }
+    __syncwarp();
+  } else if (warp < 6) {
+    // ======================= epilogue =======================
+    const int q = warp & 3;
+    const int r_local = q * 32 + lane;
+    const bool issuer = (threadIdx.x == 64);
+    uint32_t buf_phase = 0;
+    bool live = true;
+    bool stored = false;
+    for (int tile = blockIdx.x; live && tile < num_tiles; tile += gridDim.x) {
+      int mb, nb;
+      tile_coords(tile, tiles_m, tiles_n, mb, nb);
+      if (!mbar_wait(bar_tfull, buf_phase, abort_flag, p.status)) { live = false; break; }
+      tc_fence_after();
+      if (issuer && stored) bulk_wait_read0();
+      epi_bar_sync();
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+      for (int g = 0; g < BN / 32; ++g) {
+        uint32_t vh[32], vl[32];
+        tmem_ld32(t_row + g * 32, vh);
+        if (p.has_lo) tmem_ld32(t_row + BN + g * 32, vl);
+        tmem_ld_wait();
+        float o[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float v = __uint_as_float(vh[i]);
+          if (p.has_lo) v += __uint_as_float(vl[i]);
+          o[i] = v;
+        }
+        if (p.bias != nullptr) {
+          const int n0 = nb * BN + g * 32;
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (n0 + i < p.N) o[i] += __ldg(p.bias + n0 + i);
+        }
+        if constexpr (!OUT_BF16) {
+          uint8_t* piece = staging + g * (BM * 128) + r_local * 128;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            float4 v4 = make_float4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+            *reinterpret_cast<float4*>(piece + ((c ^ (r_local & 7)) << 4)) = v4;
+          }
+        } else {
+          uint8_t* piece = staging + (g >> 1) * (BM * 128) + r_local * 128;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            __nv_bfloat162 b0 = __floats2bfloat162_rn(o[8 * c], o[8 * c + 1]);
+            __nv_bfloat162 b1 = __floats2bfloat162_rn(o[8 * c + 2], o[8 * c + 3]);
+            __nv_bfloat162 b2 = __floats2bfloat162_rn(o[8 * c + 4], o[8 * c + 5]);
+            __nv_bfloat162 b3 = __floats2bfloat162_rn(o[8 * c + 6], o[8 * c + 7]);
+            uint4 v4;
+            v4.x = *reinterpret_cast<uint32_t*>(&b0);
+            v4.y = *reinterpret_cast<uint32_t*>(&b1);
+            v4.z = *reinterpret_cast<uint32_t*>(&b2);
+            v4.w = *reinterpret_cast<uint32_t*>(&b3);
+            const int cc = (g & 1) * 4 + c;
+            *reinterpret_cast<uint4*>(piece + ((cc ^ (r_local & 7)) << 4)) = v4;
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(bar_tempty);
+      fence_async_smem();
+      epi_bar_sync();
+      if (issuer) {
+        constexpr int kPieces = OUT_BF16 ? BN / 64 : BN / 32;
+        constexpr int kPieceCols = OUT_BF16 ? 64 : 32;
+#pragma unroll
+        for (int pc = 0; pc < kPieces; ++pc) {
+          const int n0 = nb * BN + pc * kPieceCols;
+          if (n0 < p.N) tma_store_2d(&tm_out, smem_u32(staging + pc * (BM * 128)), n0, mb * BM);
+        }
+        bulk_commit();
+        stored = true;
+      }
+      buf_phase ^= 1;
+    }
+    if (issuer && stored) bulk_wait0();
+  } else {
+    // ======================= converters =======================
+    const int set = (warp - 6) >> 2;                 // 0: even K stages, 1: odd K stages
+    const int r = (threadIdx.x - 192) & 127;         // row of the tile this thread owns
+    const int r0 = r & 31, r1 = r >> 5;
+    int stage = 0;
+    uint32_t phase = 0;
+    int kcount = 0;                                  // K stages seen so far (parity picks the set)
+    bool live = true;
+    for (int tile = blockIdx.x; live && tile < num_tiles; tile += gridDim.x) {
+      int mb, nb;
+      tile_coords(tile, tiles_m, tiles_n, mb, nb);
+      const int64_t row = (int64_t)mb * BM + r;
+      const bool row_ok = row < p.M;
+      const bool side = (nb == 0) && (act_out != nullptr) && row_ok;
+      for (int ks = 0; ks < p.k_stages; ++ks, ++kcount) {
+        if ((kcount & 1) == set) {
+          const int k0 = ks * 128;
+          // issue the loads before waiting for the stage: they do not touch shared memory
+          uint4 raw[16];
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            const int k = k0 + 8 * c;
+            raw[c] = (row_ok && k < p.K) ? __ldg(reinterpret_cast<const uint4*>(x + row * p.K + k)) : make_uint4(0, 0, 0, 0);
+          }
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status)) { live = false; break; }
+          uint8_t* sa = stage_base + stage * kStageBytes + r * 128;
+          uint8_t sfb[4] = {127, 127, 127, 127};
+#pragma unroll
+          for (int b = 0; b < kBlocksPerStage; ++b) {
+            float am = 0.f;
+#pragma unroll
+            for (int v = 0; v < kVecPerBlock; ++v) {
+              const uint4 w = raw[b * kVecPerBlock + v];
+              const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                am = fmaxf(am, fabsf(__uint_as_float(ws[i] << 16)));
+                am = fmaxf(am, fabsf(__uint_as_float(ws[i] & 0xFFFF0000u)));
+              }
+            }
+            const int e = block_exponent_fast<false>(am);
+            const float fwd = exp2_int(-e);
+            const bool blk_ok = (k0 + b * BS) < p.K;
+#pragma unroll
+            for (int s32 = 0; s32 < BS / 32; ++s32)
+              if (blk_ok) sfb[b * (BS / 32) + s32] = e8m0_from_exp(e);
+            if (side && blk_ok) act_exps[(int64_t)(k0 / BS + b) * p.M + row] = (int8_t)e;
+#pragma unroll
+            for (int v = 0; v < kVecPerBlock; v += 2) {
+              uint32_t cw[4];
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                const uint4 w = raw[b * kVecPerBlock + v + h];
+                const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+                float f[8];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  f[2 * i] = __fmul_rn(__uint_as_float(ws[i] << 16), fwd);
+                  f[2 * i + 1] = __fmul_rn(__uint_as_float(ws[i] & 0xFFFF0000u), fwd);
+                }
+                cw[2 * h] = encode_fp8x2<false>(f[0], f[1]) | (encode_fp8x2<false>(f[2], f[3]) << 16);
+                cw[2 * h + 1] = encode_fp8x2<false>(f[4], f[5]) | (encode_fp8x2<false>(f[6], f[7]) << 16);
+              }
+              const int c = (b * kVecPerBlock + v) >> 1;         // 16-byte chunk of the 128-byte row
+              const uint4 chunk = make_uint4(cw[0], cw[1], cw[2], cw[3]);
+              *reinterpret_cast<uint4*>(sa + ((c ^ (r & 7)) << 4)) = chunk;
+              if (side && (k0 + 16 * c) < p.K)
+                *reinterpret_cast<uint4*>(act_out + row * p.K + k0 + 16 * c) = chunk;
+            }
+          }
+          *reinterpret_cast<uint32_t*>(sf_base + stage * kSfStageBytes + r0 * 16 + r1 * 4) =
+              (uint32_t)sfb[0] | ((uint32_t)sfb[1] << 8) | ((uint32_t)sfb[2] << 16) | ((uint32_t)sfb[3] << 24);
+          fence_async_smem();                         // generic stores -> visible to the tensor core's reads
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_full + 8 * stage);
+        }
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+  }
+
+  // ======================= teardown =======================
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 20; ++i) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <int BS, bool OUT_BF16>
+int launch_fused_act(const void* x, const void* w_hi, const void* w_lo, void* out, uint8_t* act_out, int8_t* act_exps,
+                     GemmParams p, cudaStream_t stream) {
+  CUtensorMap tm_bhi, tm_blo, tm_out;
+  int rc;
+  if ((rc = make_map(&tm_bhi, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_hi, p.N, p.K, 128, BN)) != TCFP_OK) return rc;
+  if ((rc = make_map(&tm_blo, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_lo ? w_lo : w_hi, p.N, p.K, 128, BN)) != TCFP_OK) return rc;
+  if (OUT_BF16) rc = make_map(&tm_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, out, p.M, p.N, 64, BM);
+  else rc = make_map(&tm_out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, out, p.M, p.N, 32, BM);
+  if (rc != TCFP_OK) return rc;
+  p.status = device_status_ptr();
+  p.k_stages = (p.K + 127) / 128;
+  p.has_lo = w_lo != nullptr;
+  constexpr int smem = smem_bytes<KIND_MXF8, OUT_BF16>();
+  auto kern = fused_act_dual_gemm_kernel<BS, OUT_BF16>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(TCFP_ERR_UNSUPPORTED, "device index %d out of range", dev);
+  if (!configured[dev]) {
+    CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured[dev] = true;
+  }
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int grid = tiles < gemm_sm_budget() ? tiles : gemm_sm_budget();
+  kern<<<grid, kFusedThreads, smem, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), tm_bhi, tm_blo, tm_out, act_out,
+                                              act_exps, p);
+  CUDA_TRY(cudaGetLastError());
+  return TCFP_OK;
+}
+
 // The pair kernel needs at least one full 256-row tile to pay off; TCFP_GEMM_ONE_SM=1
 // forces the one-SM kernel (used by tests to cover both).
 bool use_pair_kernel(int64_t M) {
@@ -617,6 +976,40 @@ extern "C" int32_t tcfp_block_dx_gemm(const uint8_t* g, const uint8_t* sf_g, con
                                       void* stream_) {
   return block_dual_gemm_impl("block_dx_gemm", g, TCFP_E5M2, sf_g, w_hi_t, sf_hi_t, w_lo_t, sf_lo_t, nullptr, out, out_dtype,
                               M, d_in, d_out, block_size, (cudaStream_t)stream_);
+}
+
+extern "C" int32_t tcfp_block_dual_gemm_fused_act(const void* x_bf16, const uint8_t* w_hi, const uint8_t* sf_hi,
+                                                  const uint8_t* w_lo, const uint8_t* sf_lo, const float* bias,
+                                                  void* out, int32_t out_dtype, uint8_t* act_codes_out,
+                                                  int8_t* act_exps_out, int64_t M, int64_t N, int64_t K,
+                                                  int32_t block_size, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (!x_bf16 || !w_hi || !sf_hi || !out) return fail(TCFP_ERR_INVALID, "block_dual_gemm_fused_act: NULL pointer");
+  if ((w_lo == nullptr) != (sf_lo == nullptr)) return fail(TCFP_ERR_INVALID, "block_dual_gemm_fused_act: w_lo and sf_lo go together");
+  if ((act_codes_out == nullptr) != (act_exps_out == nullptr))
+    return fail(TCFP_ERR_INVALID, "block_dual_gemm_fused_act: the two side outputs go together");
+  if (block_size != 32 && block_size != 64 && block_size != 128)
+    return fail(TCFP_ERR_INVALID, "block_size must be 32, 64, or 128, got %d", block_size);
+  if (out_dtype != TCFP_F32 && out_dtype != TCFP_BF16) return fail(TCFP_ERR_INVALID, "block_dual_gemm_fused_act: output must be float32 or bfloat16");
+  int rc = check_dims("block_dual_gemm_fused_act", M, N, K);
+  if (rc != TCFP_OK) return rc;
+  if (K % block_size != 0) return fail(TCFP_ERR_INVALID, "K (%lld) must be divisible by block_size (%d)", (long long)K, block_size);
+  if (((uintptr_t)x_bf16 | (uintptr_t)sf_hi | (uintptr_t)sf_lo | (uintptr_t)act_codes_out) & 15u)
+    return fail(TCFP_ERR_INVALID, "block_dual_gemm_fused_act: activation, side output and scale-factor arrays must be 16-byte aligned");
+  GemmParams p{};
+  p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  p.a_fmt = TCFP_E4M3;
+  p.block_size = block_size;
+  p.bias = bias;
+  p.sf_hi = sf_hi; p.sf_lo = sf_lo;
+  const bool obf = out_dtype == TCFP_BF16;
+#define TCFP_FUSED(BSV)                                                                                          \
+  return obf ? launch_fused_act<BSV, true>(x_bf16, w_hi, w_lo, out, act_codes_out, act_exps_out, p, stream)       \
+             : launch_fused_act<BSV, false>(x_bf16, w_hi, w_lo, out, act_codes_out, act_exps_out, p, stream)
+  if (block_size == 32) { TCFP_FUSED(32); }
+  if (block_size == 64) { TCFP_FUSED(64); }
+  TCFP_FUSED(128);
+#undef TCFP_FUSED
 }
 
 extern "C" int32_t tcfp_bf16_dw_gemm(const void* x, const void* g_hi, const void* g_lo, void* out, int32_t out_dtype,

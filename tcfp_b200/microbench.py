@@ -8,6 +8,8 @@ sizes).  Used to time single kernels and as the target of ncu captures:
     python -m tcfp_b200.microbench qvar   [N]   # the ALU-heavy quantizer variants only (no error buffer, stochastic
                                                 # residual, per-tensor stochastic), few launches: the ncu target
     python -m tcfp_b200.microbench dx     [N]   # block dX: re-targeting pass + FP8 GEMM, and the exact bf16 route
+    python -m tcfp_b200.microbench actq   [M]   # narrow layers (N = 128..512, K = 4096): prologue-fused activation
+                                                # quantize vs block quantizer + GEMM
 """
 from __future__ import annotations
 
@@ -127,6 +129,20 @@ def dx(n: int) -> None:
               f"({4 * n**3 / ms_g / 1e9:.0f} TFLOP/s); exact bf16 route {ms_b:.3f} ms")
 
 
+def actq(m: int) -> None:
+    from .kernels import fused_act_quant_dual_gemm_forward, fused_dual_quantize_fp8
+
+    k = 4096
+    x = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
+    for bs in (32, 64, 128):
+        for n in (128, 256, 384, 512):
+            w = torch.randn(n, k, device=DEV) * 0.02
+            hi, lo, sh, sl = fused_dual_quantize_fp8(w, bs)
+            fused = timeit(lambda: fused_act_quant_dual_gemm_forward(x, hi, lo, sh, sl, bs, fuse=True), iters=10)
+            split = timeit(lambda: fused_act_quant_dual_gemm_forward(x, hi, lo, sh, sl, bs, fuse=False), iters=10)
+            print(f"block-{bs} M={m} N={n} K={k}: fused prologue {fused * 1e3:7.1f} us   quantize + GEMM {split * 1e3:7.1f} us")
+
+
 def lib(n: int) -> None:
     a, hi, lo = _fp8(n, n), _fp8(n, n), _fp8(n, n)
     s = torch.ones(1, device=DEV)
@@ -147,4 +163,4 @@ def lib(n: int) -> None:
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     size = int(sys.argv[2]) if len(sys.argv) > 2 else 8192
-    {"gemm": gemm, "block": block, "quant": quant, "lib": lib, "qvar": qvar, "dx": dx}[what](size)
+    {"gemm": gemm, "block": block, "quant": quant, "lib": lib, "qvar": qvar, "dx": dx, "actq": actq}[what](size)

@@ -281,3 +281,33 @@ def test_sm_reserve_shrinks_the_grid_not_the_result(lib):
         assert torch.equal(fused_dual_gemm_forward(pa, phi, plo, ia, ihi, ilo), full)
     assert lib.tcfp_set_sm_reserve(-1) == -1 and "sm_reserve" in _C.last_error()
     assert lib.tcfp_set_sm_reserve(500) == -1
+
+
+@pytest.mark.parametrize("bs", [32, 64, 128])
+@pytest.mark.parametrize("M,N,K", [(512, 128, 512), (384, 256, 1024), (300, 384, 256), (1000, 96, 640), (128, 512, 128)])
+def test_prologue_fused_activation_quantize_matches_the_two_kernel_route(M, N, K, bs):
+    """One kernel that block-quantizes the bf16 activation inside the GEMM's K
+    loop: its side outputs are the bytes ``block_quantize_fp8`` produces, its
+    output is the separate route's to rounding (a different kernel form sums
+    in a different order) and the oracle's within 1e-3; ragged M, N and a K
+    that ends inside a 128-wide stage included."""
+    from tcfp_b200.kernels import block_quantize_fp8, fused_act_quant_dual_gemm_forward
+
+    x = acts(500 + M, M, K, torch.bfloat16)
+    w = weights(501 + N, N, K, outliers=True)
+    hi, lo, eh, el, _ = O.dual_quantize_block(w, bs)
+    d = lambda t: t.to(DEV)  # noqa: E731
+    xd, dhi, dlo, deh, del_ = d(x), d(hi), d(lo), d(eh), d(el)
+    y_f, a_f, s_f = fused_act_quant_dual_gemm_forward(xd, dhi, dlo, deh, del_, bs, fuse=True)
+    y_s, a_s, s_s = fused_act_quant_dual_gemm_forward(xd, dhi, dlo, deh, del_, bs, fuse=False)
+    q, e = block_quantize_fp8(xd, bs)
+    assert torch.equal(a_f.view(torch.uint8), q.view(torch.uint8)) and torch.equal(s_f, e)
+    assert torch.equal(a_s.view(torch.uint8), q.view(torch.uint8)) and torch.equal(s_s, e)
+    assert rel_fro(y_f, y_s) <= 1e-5
+    a, ea = O.block_quantize(x, bs)
+    assert rel_fro(y_f, O.block_dual_gemm_nt(a, ea, hi, eh, lo, el, bs)) <= TOL
+    y2, a2, s2 = fused_act_quant_dual_gemm_forward(xd, dhi, dlo, deh, del_, bs, save_side_outputs=False, fuse=True)
+    assert a2 is None and s2 is None and torch.equal(y2, y_f)
+    bias = torch.randn(N, device=DEV)
+    y3, _, _ = fused_act_quant_dual_gemm_forward(xd, dhi, dlo, deh, del_, bs, bias=bias, out_dtype=torch.bfloat16, fuse=True)
+    assert y3.dtype == torch.bfloat16 and rel_fro(y3.float(), y_f + bias) <= 5e-3

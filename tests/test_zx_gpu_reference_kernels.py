@@ -166,6 +166,9 @@ def test_fused_act_quant_forward_and_side_outputs(ref, bs, n_out):
     y, a_own, sa_own = fused_act_quant_dual_gemm_forward(x, hi, lo, sh, sl, bs)
     assert rel_fro(y, y_ref) <= 1e-3
     assert torch.equal(u8(a_own), u8(a_ref)) and torch.equal(sa_own, sa_ref)
+    for fuse in (True, False):          # the prologue-fused kernel and the two-kernel route, whichever the default took
+        yk, ak, sk = fused_act_quant_dual_gemm_forward(x, hi, lo, sh, sl, bs, fuse=fuse)
+        assert rel_fro(yk, y_ref) <= 1e-3 and torch.equal(u8(ak), u8(a_ref)) and torch.equal(sk, sa_ref)
     q, s = block_quantize_fp8(x, bs, E4)
     assert torch.equal(u8(a_own), u8(q)) and torch.equal(sa_own, s)
     y2, a2, s2 = fused_act_quant_dual_gemm_forward(x, hi, lo, sh, sl, bs, save_side_outputs=False)
