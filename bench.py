@@ -327,7 +327,16 @@ def _train_step_extra(name: str, dev, world: int, timed, steps: int, sp: bool = 
         res["ms_per_step_collectives_off"] = ms_nocomm
         res["comm_ms_per_step"] = max(0.0, ms - ms_nocomm)
         res["collective"] = "NCCL all-reduce (bf16/fp32 partial outputs forward, input gradients backward)" if not sp \
-            else "NCCL all-gather + reduce-scatter"
+            else "NCCL all-gather (FP8 codes forward, bf16 gradients backward) + reduce-scatter"
+        # the single-GPU form of the same step, every rank running its own copy at the same time on this box
+        del step
+        torch.cuda.empty_cache()
+        with tp.single_rank():
+            step, _ = _build_train_workload(name, dev, 1, False)
+        with tp.collectives_disabled():
+            ms_single = timed(step, steps, 2) / steps
+        res["ms_per_step_single_gpu"] = ms_single
+        res["efficiency_vs_n1"] = ms_single / (world * ms)
     res["peak_mem_gb"] = torch.cuda.max_memory_allocated() / 2**30
     del step
     torch.cuda.empty_cache()

@@ -15,6 +15,11 @@
 //   SUM (block-scaled MXF8 and exactly dequantized BF16; no epilogue factors):
 //       two MMAs 256 x 128 per K step into the SAME 128 accumulator columns;
 //       each CTA stages 64 rows of W_hi and 64 rows of W_lo.
+//   A single bf16 product (the weight gradient of a bf16 output gradient) has
+//   no second operand to sum, and a 256 x 128 tile would pull 24 KB per CTA
+//   from L2 for every four MMAs (96 B per clock per SM, more than L2 delivers):
+//   it runs in the CONCAT layout as a 256 x 256 tile (KIND_BF16_WIDE, 64 B per
+//   clock per SM, the same as the dual kinds).
 //
 // Roles per CTA as in the one-SM kernel (warp 0 TMA, warp 1 MMA/TMEM, warps
 // 2-5 epilogue).  Both producers signal the LEADER's full barrier; the
@@ -41,6 +46,9 @@ constexpr int kStageBytes = kATile + kBTile;
 constexpr int kSfStage = 3 * 512;
 constexpr int kPieceBytes = 16384;    // 128 rows x 128 B of staged output
 constexpr int kGroupM = 8;            // default rasterisation group, in units of 256-row tile rows
+constexpr int KIND_BF16_WIDE = 3;     // bf16 operands, CONCAT layout (single product, 256 x 256 tile)
+
+__host__ __device__ constexpr bool is_bf16_kind(int kind) { return kind == KIND_BF16 || kind == KIND_BF16_WIDE; }
 
 struct Gemm2Params {
   int M, N, K;
@@ -107,7 +115,7 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t adesc, uin
         "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum)
         : "memory");
-  } else if constexpr (KIND == KIND_BF16) {
+  } else if constexpr (is_bf16_kind(KIND)) {
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
@@ -124,8 +132,8 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t adesc, uin
 
 template <int KIND>
 struct Traits2 {
-  static constexpr bool kSum = (KIND != KIND_F8);
-  static constexpr int kElemBytes = (KIND == KIND_BF16) ? 2 : 1;
+  static constexpr bool kSum = (KIND == KIND_MXF8 || KIND == KIND_BF16);
+  static constexpr int kElemBytes = is_bf16_kind(KIND) ? 2 : 1;
   static constexpr int kStageK = 128 / kElemBytes;
   static constexpr int kMmaK = 32 / kElemBytes;
   static constexpr int kStages = (KIND == KIND_MXF8) ? 5 : 6;
@@ -250,8 +258,15 @@ dual_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
             // this CTA's half of the 256 MMA columns
             const CUtensorMap* map = (p.has_lo && rank == 1) ? &tm_blo : &tm_bhi;
             const int n0 = nb * tile_n + ((!p.has_lo && rank == 1) ? BN : 0);
-            if constexpr (!B_MN) tma_load_2d_pair(sb, map, k0, n0, full_leader);
-            else tma_load_2d_pair(sb, map, n0, k0, full_leader);
+            if constexpr (!B_MN) {
+              tma_load_2d_pair(sb, map, k0, n0, full_leader);
+            } else {
+              // (K, N) row-major: one box per 128-byte-wide group of this CTA's 128 columns
+              constexpr int kBBoxes = T::kElemBytes;
+#pragma unroll
+              for (int b = 0; b < kBBoxes; ++b)
+                tma_load_2d_pair(sb + b * (kBTile / kBBoxes), map, n0 + b * (128 / T::kElemBytes), k0, full_leader);
+            }
           } else {
             // 64 of the 128 MMA columns of each operand
             const int n0 = nb * BN + (int)rank * (BN / 2);
@@ -285,8 +300,8 @@ dual_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
         idesc = ((uint32_t)p.a_fmt << 7) | ((B_MN ? 1u : 0u) << 16) | ((n_mma >> 3) << 17) | (1u << 23) |
                 ((uint32_t)((2 * BM) >> 4) << 24);
       } else {
-        const uint32_t fa = (KIND == KIND_BF16) ? 1u : (uint32_t)p.a_fmt;
-        const uint32_t fb = (KIND == KIND_BF16) ? 1u : 0u;
+        const uint32_t fa = is_bf16_kind(KIND) ? 1u : (uint32_t)p.a_fmt;
+        const uint32_t fb = is_bf16_kind(KIND) ? 1u : 0u;
         idesc = (1u << 4) | (fa << 7) | (fb << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
                 ((n_mma >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
       }
@@ -295,8 +310,9 @@ dual_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_con
       constexpr uint32_t kAKStep = A_MN ? (uint32_t)(T::kMmaK * 128) : 32u;
       // B: every CTA holds (n_mma / 2) columns of each MMA's B operand.
       //   K-major : rows of 128 B, 8-row groups 1024 B apart.
-      //   MN-major: one 128-byte-wide column group (CONCAT fp8: 128 cols; SUM bf16: 64 cols); LBO unused.
-      constexpr uint32_t kBLbo = 16u;
+      //   MN-major: 128-byte-wide column groups (CONCAT fp8: one of 128 cols; SUM bf16: one of 64 cols;
+      //             CONCAT bf16: two of 64 cols, LBO apart).
+      constexpr uint32_t kBLbo = (B_MN && !kSum && T::kElemBytes == 2) ? (uint32_t)(kBTile / 2) : 16u;
       constexpr uint32_t kBKStep = B_MN ? (uint32_t)(T::kMmaK * 128) : 32u;
       int stage = 0;
       uint32_t phase = 0;
@@ -540,7 +556,7 @@ template <int KIND, bool B_MN, bool OUT_BF16, bool A_MN = false>
 int launch2(const void* a, const void* b_hi, const void* b_lo, const void* sf_a, const void* sf_hi, const void* sf_lo,
             void* out, Gemm2Params p, cudaStream_t stream) {
   using T = Traits2<KIND>;
-  const CUtensorMapDataType dt = (KIND == KIND_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  const CUtensorMapDataType dt = is_bf16_kind(KIND) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
   const int eb = T::kElemBytes;
   const CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_128B;
   CUtensorMap tm_a, tm_bhi, tm_blo, tm_out, tm_sfa, tm_sfhi, tm_sflo;
@@ -553,9 +569,10 @@ int launch2(const void* a, const void* b_hi, const void* b_lo, const void* sf_a,
     if ((rc = make_map2(&tm_bhi, dt, eb, b_hi, p.N, p.K, T::kStageK, b_rows, sw)) != TCFP_OK) return rc;
     if ((rc = make_map2(&tm_blo, dt, eb, b_lo ? b_lo : b_hi, p.N, p.K, T::kStageK, b_rows, sw)) != TCFP_OK) return rc;
   } else {
-    if (b_rows * eb != 128) return fail(TCFP_ERR_UNSUPPORTED, "pair kernel: this operand layout is not tiled");
-    if ((rc = make_map2(&tm_bhi, dt, eb, b_hi, p.K, p.N, b_rows, T::kStageK, sw)) != TCFP_OK) return rc;
-    if ((rc = make_map2(&tm_blo, dt, eb, b_lo ? b_lo : b_hi, p.K, p.N, b_rows, T::kStageK, sw)) != TCFP_OK) return rc;
+    // boxes are one 128-byte swizzle row wide; a CTA whose share is 256 bytes wide loads two
+    if ((b_rows * eb) % 128 != 0) return fail(TCFP_ERR_UNSUPPORTED, "pair kernel: this operand layout is not tiled");
+    if ((rc = make_map2(&tm_bhi, dt, eb, b_hi, p.K, p.N, 128 / eb, T::kStageK, sw)) != TCFP_OK) return rc;
+    if ((rc = make_map2(&tm_blo, dt, eb, b_lo ? b_lo : b_hi, p.K, p.N, 128 / eb, T::kStageK, sw)) != TCFP_OK) return rc;
   }
   if (OUT_BF16) rc = make_map2(&tm_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, out, p.M, p.N, 64, BM, sw);
   else rc = make_map2(&tm_out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, out, p.M, p.N, 32, BM, sw);
@@ -625,6 +642,9 @@ int pair_gemm_dispatch(int kind, bool a_mn, bool b_mn, bool out_bf16, const void
                   : launch2<KIND, BMN, false>(a, b_hi, b_lo, sf_a, sf_hi, sf_lo, out, p, stream)
   if (a_mn) {
     if (!b_mn || kind == KIND_MXF8) return fail(TCFP_ERR_UNSUPPORTED, "pair kernel: transposed A is built for the weight gradients only");
+    if (kind == KIND_BF16 && b_lo == nullptr)
+      return out_bf16 ? launch2<KIND_BF16_WIDE, true, true, true>(a, b_hi, b_lo, sf_a, sf_hi, sf_lo, out, p, stream)
+                      : launch2<KIND_BF16_WIDE, true, false, true>(a, b_hi, b_lo, sf_a, sf_hi, sf_lo, out, p, stream);
     if (kind == KIND_BF16)
       return out_bf16 ? launch2<KIND_BF16, true, true, true>(a, b_hi, b_lo, sf_a, sf_hi, sf_lo, out, p, stream)
                       : launch2<KIND_BF16, true, false, true>(a, b_hi, b_lo, sf_a, sf_hi, sf_lo, out, p, stream);

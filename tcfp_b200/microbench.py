@@ -143,6 +143,21 @@ def actq(m: int) -> None:
             print(f"block-{bs} M={m} N={n} K={k}: fused prologue {fused * 1e3:7.1f} us   quantize + GEMM {split * 1e3:7.1f} us")
 
 
+def dw(tokens: int) -> None:
+    """Weight gradient of a bf16 output gradient (one bf16 product, both operands
+    read in their forward layouts) at the decoder layer's four shapes."""
+    from .kernels import bf16_weight_grad
+
+    for d_out, d_in in ((12288, 4096), (4096, 4096), (22016, 4096), (4096, 11008), (8192, 8192)):
+        g = torch.randn(tokens, d_out, device=DEV, dtype=torch.bfloat16)
+        x = torch.randn(tokens, d_in, device=DEV, dtype=torch.bfloat16)
+        ms = timeit(lambda: bf16_weight_grad(g, x), iters=10)
+        ms_lib = timeit(lambda: g.t() @ x, iters=10)
+        fl = 2.0 * tokens * d_out * d_in
+        print(f"dW bf16 tokens={tokens} {d_out}x{d_in}: {ms:.3f} ms {fl / ms / 1e9:.0f} TFLOP/s   "
+              f"(torch bf16 matmul, bf16 output: {ms_lib:.3f} ms {fl / ms_lib / 1e9:.0f} TFLOP/s)")
+
+
 def lib(n: int) -> None:
     a, hi, lo = _fp8(n, n), _fp8(n, n), _fp8(n, n)
     s = torch.ones(1, device=DEV)
@@ -163,4 +178,4 @@ def lib(n: int) -> None:
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     size = int(sys.argv[2]) if len(sys.argv) > 2 else 8192
-    {"gemm": gemm, "block": block, "quant": quant, "lib": lib, "qvar": qvar, "dx": dx, "actq": actq}[what](size)
+    {"gemm": gemm, "block": block, "quant": quant, "lib": lib, "qvar": qvar, "dx": dx, "actq": actq, "dw": dw}[what](size)

@@ -70,9 +70,29 @@ class LayerHooks:
     asynchronous in-place reduction of it; ``dx_hook(grad_input)`` is called
     with the input gradient before the weight gradient is computed.  Both
     return ``None`` or an object whose ``wait()`` makes the current stream
-    wait for the collective."""
+    wait for the collective.
 
-    def __init__(self, out_hook=None, row_chunks: int = 1, dx_hook=None, reserve_sms: int = 0):
+    ``sp`` (sequence parallelism) turns the layer's input into this rank's
+    TOKEN SHARD, a 2-D ``(tokens / world, K)`` matrix: the Function quantizes
+    the shard, calls ``sp.gather_rows`` on the FP8 codes (one byte per element
+    on the wire instead of two) and ``sp.gather_planes`` on the exponent planes
+    -- the per-tensor Function, whose scale needs the global amax, gathers the
+    input itself -- and the output covers all tokens.  Backward,
+    ``sp.scatter_rows_async(dX)`` starts the reduce-scatter of the full input
+    gradient and returns ``(handle, this rank's rows)``; the weight gradient is
+    computed while it runs.
+
+    ``sp_out`` is the mirror image for a layer whose OUTPUT is reduced over
+    ranks and sharded over tokens: the forward output goes through
+    ``sp_out.scatter_rows_async`` and the layer returns this rank's rows.
+    Backward it receives the gradient of those rows; with block scaling it
+    quantizes them, gathers the E5M2 codes and exponents for the dX GEMM, and
+    gathers the full-precision gradient the weight gradient needs with
+    ``sp_out.gather_rows_async`` while the dX GEMM runs."""
+
+    def __init__(self, out_hook=None, row_chunks: int = 1, dx_hook=None, reserve_sms: int = 0, sp=None, sp_out=None):
+        self.sp = sp
+        self.sp_out = sp_out
         self.out_hook = out_hook
         self.row_chunks = max(1, int(row_chunks))
         self.dx_hook = dx_hook
@@ -176,6 +196,9 @@ class _TCFP12TensorCoreFunction(torch.autograd.Function):
 
         input_shape = input.shape
         x2d = _flat2d(input)
+        sp = None if hooks is None else hooks.sp
+        if sp is not None:
+            x2d = sp.gather_rows(x2d.contiguous())               # the scale below is the amax over all tokens
         act_fp8, act_inv = to_fp8_e4m3(x2d)                      # always fresh (:390)
         bias_f = None if bias is None else bias.detach().float().contiguous()
         out2d = torch.empty((x2d.shape[0], w_hi.shape[0]), device=x2d.device, dtype=out_dtype)
@@ -186,7 +209,12 @@ class _TCFP12TensorCoreFunction(torch.autograd.Function):
             if hooks is not None and hooks.out_hook is not None:
                 pending.append(hooks.out_hook(out2d[r0:r1]))
         _wait_all(pending)
+        sp_out = None if hooks is None else hooks.sp_out
+        if sp_out is not None:
+            handle, out2d = sp_out.scatter_rows_async(out2d)
+            _wait_all([handle])
         ctx.dx_hook = None if hooks is None else hooks.dx_hook
+        ctx.sp, ctx.sp_out = sp, sp_out
         ctx.reserve_sms = 0 if hooks is None else hooks.reserve_sms
         ctx.dx_dtype = _dx_dtype(input)
         ctx.hp_grad_weight = hp_grad_weight
@@ -198,6 +226,8 @@ class _TCFP12TensorCoreFunction(torch.autograd.Function):
             saved += [w_lo, inv_lo]
         saved += [inv_hi, act_inv]
         ctx.save_for_backward(*saved)
+        if sp is not None or sp_out is not None:
+            return out2d
         return out2d.reshape(*input_shape[:-1], out2d.shape[-1])
 
     @staticmethod
@@ -211,6 +241,8 @@ class _TCFP12TensorCoreFunction(torch.autograd.Function):
         g2d = _flat2d(grad_output)
         if g2d.dtype not in (torch.float32, torch.bfloat16):
             g2d = g2d.float()
+        if ctx.sp_out is not None:
+            g2d = ctx.sp_out.gather_rows(g2d)          # the gradient's scale is the amax over all tokens
         # always fresh (:494); with a bias its gradient (the column sums, :558) comes out of the same passes
         grad_bias = None
         if ctx.has_bias and g2d.shape[1] % 8 == 0:
@@ -221,7 +253,11 @@ class _TCFP12TensorCoreFunction(torch.autograd.Function):
                 grad_bias = g2d.float().sum(dim=0)
         grad_input = fused_dual_gemm_backward_dx(grad_fp8, w_hi, w_lo, grad_inv, inv_hi, inv_lo,
                                                  out_dtype=ctx.dx_dtype)
-        dx_pending = ctx.dx_hook(grad_input) if ctx.dx_hook is not None else None   # overlaps the dW GEMM below
+        # either collective overlaps the dW GEMM below
+        if ctx.sp is not None:
+            dx_pending, grad_input = ctx.sp.scatter_rows_async(grad_input)
+        else:
+            dx_pending = ctx.dx_hook(grad_input) if ctx.dx_hook is not None else None
         grad_input = grad_input.reshape(ctx.input_shape)
         with _C.sm_reserve(ctx.reserve_sms if dx_pending is not None else 0):
             if ctx.hp_grad_weight:
@@ -262,8 +298,15 @@ class _TCFP12BlockScaledFunction(torch.autograd.Function):
         if x2d.dtype not in (torch.float32, torch.bfloat16):
             x2d = x2d.float()
         act_fp8, act_scales = block_quantize_fp8(x2d, bs, torch.float8_e4m3fn)
+        sp = None if hooks is None else hooks.sp
+        if sp is not None:
+            # block scales are local to a row: quantize this rank's tokens, gather codes and exponents
+            act_fp8 = sp.gather_rows(act_fp8)
+            act_scales = sp.gather_planes(act_scales)
+            if hp_grad_weight:
+                x2d = sp.gather_rows(x2d.contiguous())
         bias_f = None if bias is None else bias.detach().float().contiguous()
-        M, K = x2d.shape
+        M, K = act_fp8.shape
         out2d = torch.empty((M, w_hi.shape[0]), device=x2d.device, dtype=out_dtype)
         act_sf = pack_block_scales(act_scales, bs)
         pending = []
@@ -274,7 +317,12 @@ class _TCFP12BlockScaledFunction(torch.autograd.Function):
             if hooks is not None and hooks.out_hook is not None:
                 pending.append(hooks.out_hook(out2d[r0:r1]))
         _wait_all(pending)
+        sp_out = None if hooks is None else hooks.sp_out
+        if sp_out is not None:
+            handle, out2d = sp_out.scatter_rows_async(out2d)
+            _wait_all([handle])
         ctx.dx_hook = None if hooks is None else hooks.dx_hook
+        ctx.sp, ctx.sp_out = sp, sp_out
         ctx.reserve_sms = 0 if hooks is None else hooks.reserve_sms
         ctx.dx_dtype = _dx_dtype(input)
         ctx.hp_grad_weight = hp_grad_weight
@@ -289,6 +337,8 @@ class _TCFP12BlockScaledFunction(torch.autograd.Function):
         if not abd:
             saved += [w_lo, s_lo]
         ctx.save_for_backward(*saved)
+        if sp is not None or sp_out is not None:
+            return out2d
         return out2d.reshape(*input_shape[:-1], out2d.shape[-1])
 
     @staticmethod
@@ -308,14 +358,32 @@ class _TCFP12BlockScaledFunction(torch.autograd.Function):
             g2d = g2d.float()
         # E5M2 block quantize of the gradient along D_out (:724-726); dX on the FP8 block-scaled MMA against
         # the weight re-targeted for this contraction (once per weight version, kept on w_hi)
-        if ctx.has_bias:        # the bias gradient (column sums, :753) rides the quantizer's pass
+        g_pending = None
+        if ctx.sp_out is not None:
+            # g2d holds this rank's tokens: quantize them, gather codes and exponents for dX, and fetch the
+            # full-precision rows of the other ranks (dW needs them) while the dX GEMM runs
+            grad_fp8, grad_scales = block_quantize_fp8(g2d, bs, torch.float8_e5m2)
+            grad_fp8 = ctx.sp_out.gather_rows(grad_fp8)
+            grad_scales = ctx.sp_out.gather_planes(grad_scales)
+            g_pending, g2d = ctx.sp_out.gather_rows_async(g2d)
+            grad_bias = None
+        elif ctx.has_bias:      # the bias gradient (column sums, :753) rides the quantizer's pass
             grad_fp8, grad_scales, grad_bias = block_quantize_fp8(g2d, bs, torch.float8_e5m2, want_colsum=True)
         else:
             grad_fp8, grad_scales = block_quantize_fp8(g2d, bs, torch.float8_e5m2)
             grad_bias = None
-        grad_input = fused_block_scaled_backward_dx(grad_fp8, w_hi, w_lo, grad_scales, s_hi, s_lo, bs,
-                                                    out_dtype=ctx.dx_dtype)
-        dx_pending = ctx.dx_hook(grad_input) if ctx.dx_hook is not None else None   # overlaps the dW GEMM below
+        with _C.sm_reserve(ctx.reserve_sms if g_pending is not None else 0):
+            grad_input = fused_block_scaled_backward_dx(grad_fp8, w_hi, w_lo, grad_scales, s_hi, s_lo, bs,
+                                                        out_dtype=ctx.dx_dtype)
+        if ctx.sp_out is not None:
+            _wait_all([g_pending])
+            if ctx.has_bias:
+                grad_bias = g2d.float().sum(dim=0)
+        # either collective overlaps the dW GEMM below
+        if ctx.sp is not None:
+            dx_pending, grad_input = ctx.sp.scatter_rows_async(grad_input)
+        else:
+            dx_pending = ctx.dx_hook(grad_input) if ctx.dx_hook is not None else None
         grad_input = grad_input.reshape(ctx.input_shape)
         # dW in full precision, as in the reference (:744-750)
         with _C.sm_reserve(ctx.reserve_sms if dx_pending is not None else 0):

@@ -56,6 +56,35 @@ class collectives_disabled:
         return False
 
 
+_FORCE_SINGLE = False
+
+
+class single_rank:
+    """Measurement aid: layers constructed inside this context are built
+    unsharded (world size 1) even under ``torch.distributed``, so that a
+    multi-GPU run can time the single-GPU form of its own workload on the same
+    box (run it under ``collectives_disabled()``: the hooks of such layers
+    would otherwise still address the process group)."""
+
+    def __enter__(self):
+        global _FORCE_SINGLE
+        self._prev = _FORCE_SINGLE
+        _FORCE_SINGLE = True
+        return self
+
+    def __exit__(self, *exc):
+        global _FORCE_SINGLE
+        _FORCE_SINGLE = self._prev
+        return False
+
+
+def world_and_rank(group=None) -> tuple[int, int]:
+    """(world size, rank) the tensor-parallel layers shard by."""
+    if _FORCE_SINGLE or not dist.is_initialized():
+        return 1, 0
+    return dist.get_world_size(group), dist.get_rank(group)
+
+
 def _active(group) -> bool:
     return _COLLECTIVES_ENABLED and dist.is_initialized() and dist.get_world_size(group) > 1
 
@@ -223,6 +252,80 @@ def _all_reduce_async(t: torch.Tensor, group):
     return _Pending(dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group, async_op=True))
 
 
+class _Pending2(_Pending):
+    """A pending collective that also keeps its input alive until waited for."""
+
+    def __init__(self, work, keep):
+        super().__init__(work)
+        self.keep = keep
+
+    def wait(self):
+        super().wait()
+        self.keep = None
+
+
+class SequenceParallelIO:
+    """The collectives of a layer whose input is this rank's token shard
+    (``nn.LayerHooks.sp``): all-gather of row-sharded matrices -- FP8 codes go
+    over the wire as bytes -- and of the ``(K / bs, rows)`` exponent planes,
+    and the asynchronous reduce-scatter of the full input gradient."""
+
+    def __init__(self, group=None):
+        self.group = group
+
+    def _world(self) -> int:
+        return dist.get_world_size(self.group) if dist.is_initialized() else 1
+
+    def gather_rows(self, t: torch.Tensor) -> torch.Tensor:
+        if self._world() == 1:
+            return t
+        t = t.contiguous()
+        wire = t.view(torch.uint8) if t.element_size() == 1 else t        # NCCL has no FP8 type; bytes are bytes
+        return _all_gather_rows(wire, self.group).view(t.dtype)
+
+    def gather_rows_async(self, t: torch.Tensor):
+        """Starts the all-gather of a row-sharded matrix; returns ``(handle
+        or None, gathered matrix)``, valid once the handle has been waited for."""
+        world = self._world()
+        if world == 1:
+            return None, t
+        if not _COLLECTIVES_ENABLED or not t.is_cuda:
+            return None, self.gather_rows(t)
+        t = t.contiguous()
+        out = torch.empty((t.shape[0] * world,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+        work = dist.all_gather_into_tensor(out, t, group=self.group, async_op=True)
+        return _Pending2(work, t), out
+
+    def gather_planes(self, planes: torch.Tensor) -> torch.Tensor:
+        """``(P, rows_local)`` -> ``(P, rows)``: the row index is the fast dimension of a plane."""
+        world = self._world()
+        if world == 1:
+            return planes
+        P, r = planes.shape
+        g = _all_gather_rows(planes.contiguous(), self.group)             # (world * P, r), rank-major
+        return g.view(world, P, r).permute(1, 0, 2).reshape(P, world * r)
+
+    def scatter_rows_async(self, full: torch.Tensor):
+        """Starts ``reduce_scatter(full)`` over the token dimension; returns
+        ``(handle or None, this rank's rows)``.  The rows are valid once the
+        handle has been waited for."""
+        world = self._world()
+        if world == 1:
+            return None, full
+        rank = dist.get_rank(self.group)
+        if full.shape[0] % world != 0:
+            raise ValueError(f"sequence parallelism needs the token count ({full.shape[0]}) to be a multiple of the "
+                             f"tensor-parallel world size ({world})")
+        rows = full.shape[0] // world
+        if not _COLLECTIVES_ENABLED or not full.is_cuda:
+            # measurement aid (unreduced rows), or gloo on CPU, which has no reduce-scatter
+            return None, _reduce_scatter_rows(full, self.group)
+        full = full.contiguous()
+        out = torch.empty((rows,) + tuple(full.shape[1:]), dtype=full.dtype, device=full.device)
+        work = dist.reduce_scatter_tensor(out, full, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+        return _Pending2(work, full), out
+
+
 class ColumnParallelLinear(nn.Module):
     """``y_local = x @ W[rows of this rank].T``; output stays sharded.
 
@@ -233,18 +336,27 @@ class ColumnParallelLinear(nn.Module):
     part, and a single input-gradient all-reduce.  ``forward`` then returns a
     tuple of the parts' local outputs.  Scale blocks are per weight row, so
     the fused layer's quantized bytes are those of the separate layers.
+
+    ``sequence_parallel=True``: the input is this rank's token shard
+    ``(tokens / world, in_features)`` and the output covers all tokens.  A
+    ``TCFPLinear`` inside gathers the activation AFTER quantizing it (FP8
+    codes and exponents on the wire, the quantizer runs on tokens / world
+    rows) and reduce-scatters the input gradient under its weight-gradient
+    GEMM; any other layer gets a plain all-gather in front.
     """
 
     def __init__(self, in_features: int, out_features, bias: bool = True, *, group=None, granule: int = 16,
                  layer_factory: Callable[..., nn.Module] = _default_factory, reduce_input_grad: bool = True,
-                 comm_sms: int = 32, **layer_kw):
+                 comm_sms: int = 32, sequence_parallel: bool = False, **layer_kw):
         super().__init__()
         self.group = group
+        self.sequence_parallel = sequence_parallel
+        if sequence_parallel:
+            reduce_input_grad = False      # the reduce-scatter of the token shards is the reduction
         # several column-parallel layers fed by one tensor may share a single gradient all-reduce:
         # the caller applies copy_to_parallel once and turns this off
         self.reduce_input_grad = reduce_input_grad
-        world = dist.get_world_size(group) if dist.is_initialized() else 1
-        rank = dist.get_rank(group) if dist.is_initialized() else 0
+        world, rank = world_and_rank(group)
         self.fused = isinstance(out_features, (tuple, list))
         parts = tuple(out_features) if self.fused else (out_features,)
         self.bounds = [shard_bounds(n, world, rank, granule) for n in parts]
@@ -259,8 +371,15 @@ class ColumnParallelLinear(nn.Module):
 
             # the weight-gradient GEMM leaves `comm_sms` SMs to NCCL while the input gradient is being reduced
             self.inner._hooks = LayerHooks(dx_hook=lambda g: _all_reduce_async(g, self.group), reserve_sms=comm_sms)
+        self._sp_fused = sequence_parallel and world > 1 and _is_tcfp(self.inner)
+        if self._sp_fused:
+            from .nn import LayerHooks
+
+            self.inner._hooks = LayerHooks(sp=SequenceParallelIO(group), reserve_sms=comm_sms)
 
     def forward(self, x: torch.Tensor):
+        if self.sequence_parallel and not self._sp_fused:
+            x = _GatherFromSequenceParallel.apply(x, self.group)
         if self.reduce_input_grad and not self._overlap:
             x = _CopyToParallel.apply(x, self.group)
         y = self.inner(x)
@@ -288,13 +407,12 @@ class RowParallelLinear(nn.Module):
 
     def __init__(self, in_features: int, out_features: int, bias: bool = True, *, group=None, granule: int = 16,
                  layer_factory: Callable[..., nn.Module] = _default_factory, reduce_dtype: torch.dtype | None = None,
-                 sequence_parallel: bool = False, overlap_chunks: int = 1, **layer_kw):
+                 sequence_parallel: bool = False, overlap_chunks: int = 1, comm_sms: int = 32, **layer_kw):
         super().__init__()
         self.group = group
         # with sequence parallelism the output is reduce-scattered over tokens instead of all-reduced
         self.sequence_parallel = sequence_parallel
-        world = dist.get_world_size(group) if dist.is_initialized() else 1
-        rank = dist.get_rank(group) if dist.is_initialized() else 0
+        world, rank = world_and_rank(group)
         self.in_start, self.in_end = shard_bounds(in_features, world, rank, granule)
         self.in_features, self.out_features = in_features, out_features
         self.reduce_dtype = reduce_dtype
@@ -312,10 +430,18 @@ class RowParallelLinear(nn.Module):
 
             self.inner._hooks = LayerHooks(out_hook=lambda y: _all_reduce_async(y, self.group),
                                            row_chunks=overlap_chunks)
+        # sequence parallel with a TCFPLinear inside: the reduce-scatter of the output and the gathers of the
+        # output gradient (FP8 codes for dX, full precision under the dX GEMM for dW) happen inside the layer
+        self._sp_fused = (_is_tcfp(self.inner) and sequence_parallel and world > 1
+                          and (reduce_dtype is None or reduce_dtype == inner_dtype))
+        if self._sp_fused:
+            from .nn import LayerHooks
+
+            self.inner._hooks = LayerHooks(sp_out=SequenceParallelIO(group), reserve_sms=comm_sms)
 
     def forward(self, x_shard: torch.Tensor) -> torch.Tensor:
         y = self.inner(x_shard)
-        if not self._overlap:
+        if not self._overlap and not self._sp_fused:
             if self.reduce_dtype is not None and y.dtype != self.reduce_dtype:
                 y = y.to(self.reduce_dtype)        # bf16 on the wire halves the NVLink bytes
             if self.sequence_parallel:
@@ -345,7 +471,7 @@ class ParallelMLP(nn.Module):
         self.group = group
         self.sequence_parallel = sequence_parallel
         self.up = ColumnParallelLinear(d_model, d_hidden, bias, group=group, granule=granule,
-                                       layer_factory=layer_factory, reduce_input_grad=not sequence_parallel,
+                                       layer_factory=layer_factory, sequence_parallel=sequence_parallel,
                                        **layer_kw)
         self.down = RowParallelLinear(d_hidden, d_model, bias, group=group, granule=granule,
                                       layer_factory=layer_factory, reduce_dtype=reduce_dtype,
@@ -353,6 +479,4 @@ class ParallelMLP(nn.Module):
         self.activation = activation
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        if self.sequence_parallel:
-            x = _GatherFromSequenceParallel.apply(x, self.group)
         return self.down(self.activation(self.up(x)))

@@ -10,11 +10,12 @@ import torch.distributed as dist
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .tp import ColumnParallelLinear, ParallelMLP, RowParallelLinear, gather_from_sequence_parallel
+from .tp import (ColumnParallelLinear, ParallelMLP, RowParallelLinear, gather_from_sequence_parallel,
+                 world_and_rank)
 
 
 def _world() -> int:
-    return dist.get_world_size() if dist.is_initialized() else 1
+    return world_and_rank()[0]
 
 
 class RMSNorm(nn.Module):
@@ -38,8 +39,10 @@ class DecoderLayer(nn.Module):
     gradients of the column-parallel groups are all-reduced under their
     weight-gradient GEMMs.  ``sequence_parallel=True``: activations between the
     blocks are sharded over tokens -- norms and residual adds touch tokens /
-    world rows -- with an all-gather before each column-parallel group and a
-    reduce-scatter after each row-parallel layer (same bytes on the wire)."""
+    world rows -- each column-parallel group all-gathers its input as FP8 codes
+    after quantizing this rank's tokens and reduce-scatters its input gradient
+    under the weight-gradient GEMM; each row-parallel layer reduce-scatters its
+    output and all-gathers its output gradient."""
 
     def __init__(self, d_model: int, n_heads: int, ffn: int, *, granule: int = 64, sequence_parallel: bool = False,
                  overlap_chunks: int = 1, **layer_kw):
@@ -52,30 +55,24 @@ class DecoderLayer(nn.Module):
         g_attn = max(granule, self.head_dim)
         self.norm1 = RMSNorm(d_model)
         self.qkv = ColumnParallelLinear(d_model, (d_model, d_model, d_model), bias=False, granule=g_attn,
-                                        reduce_input_grad=not self.sp, **layer_kw)
+                                        sequence_parallel=self.sp, **layer_kw)
         self.o = RowParallelLinear(d_model, d_model, bias=False, granule=g_attn, reduce_dtype=torch.bfloat16,
                                    sequence_parallel=self.sp, overlap_chunks=overlap_chunks, **layer_kw)
         self.norm2 = RMSNorm(d_model)
         self.gate_up = ColumnParallelLinear(d_model, (ffn, ffn), bias=False, granule=granule,
-                                            reduce_input_grad=not self.sp, **layer_kw)
+                                            sequence_parallel=self.sp, **layer_kw)
         self.down = RowParallelLinear(ffn, d_model, bias=False, granule=granule, reduce_dtype=torch.bfloat16,
                                       sequence_parallel=self.sp, overlap_chunks=overlap_chunks, **layer_kw)
 
     def forward(self, x):                      # x: (B, T, d) bf16; with sequence parallelism (B*T/world, d)
         B, T = self.batch_shape if self.sp else x.shape[:2]
-        h = self.norm1(x)
-        if self.sp:
-            h = gather_from_sequence_parallel(h)
-        q, k, v = self.qkv(h)
+        q, k, v = self.qkv(self.norm1(x))          # sequence parallel: the layer gathers its (quantized) input
         shp = (B, T, self.heads_local, self.head_dim)
         a = F.scaled_dot_product_attention(q.reshape(shp).transpose(1, 2), k.reshape(shp).transpose(1, 2),
                                            v.reshape(shp).transpose(1, 2), is_causal=True)
         a = a.transpose(1, 2).reshape(q.shape[:-1] + (self.heads_local * self.head_dim,))
         x = x + self.o(a)
-        h = self.norm2(x)
-        if self.sp:
-            h = gather_from_sequence_parallel(h)
-        gate, up = self.gate_up(h)
+        gate, up = self.gate_up(self.norm2(x))
         return x + self.down(F.silu(gate) * up)
 
 

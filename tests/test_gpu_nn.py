@@ -237,6 +237,11 @@ def test_bf16_weight_grad_bf16_gradient_and_bf16_layer_output():
     x = acts(63, 640, 384, torch.bfloat16)
     out = bf16_weight_grad(g.to(DEV), x.to(DEV))
     assert out.is_contiguous() and rel_fro(out, g.double().t() @ x.double()) <= 2e-5
+    # the single product runs as 256 x 256 tiles: ragged edges in every dimension, several tiles, long K
+    for M, N, K in [(1000, 640, 320), (520, 384, 200), (4160, 768, 520), (264, 256, 256)]:
+        g2, x2 = acts(64, M, N, torch.bfloat16), acts(65, M, K, torch.bfloat16)
+        out = bf16_weight_grad(g2.to(DEV), x2.to(DEV))
+        assert out.shape == (N, K) and rel_fro(out, g2.double().t() @ x2.double()) <= 2e-5, (M, N, K)
     layer = TCFPLinear(384, 256, use_tensor_cores=True, scale_block_size=64, out_dtype=torch.bfloat16).to(DEV)
     xin = x.to(DEV).requires_grad_(True)
     y = layer(xin)
@@ -483,6 +488,142 @@ def test_layer_hooks_chunk_the_forward_and_see_the_input_gradient_first(kw):
     y.backward(g)
     assert seen["dx"] == [(1000, 256)] and all(h.waited for h in handles)
     assert torch.equal(x2.grad, 2.0 * x1.grad) and torch.equal(hooked.weight.grad, plain.weight.grad)
+
+
+@pytest.mark.parametrize("kw", [dict(scale_block_size=64), dict(scale_block_size=32, hp_grad_weight=True), dict()],
+                         ids=["block64", "block32_hp_grad", "per_tensor"])
+def test_sequence_parallel_hooks_gather_after_quantizing_and_scatter_the_input_gradient(kw):
+    """``LayerHooks.sp``: the layer's input is one rank's token shard.  With
+    block scaling the shard is quantized first and the FP8 codes and exponent
+    planes are gathered (scale blocks are local to a row, so the gathered bytes
+    are those of quantizing all tokens); with per-tensor scaling the input is
+    gathered before quantizing.  Backward the full input gradient goes to
+    ``scatter_rows_async`` before the weight gradient is computed.  Two ranks
+    with equal weights are emulated on one GPU: the peer's shard is quantized
+    here, and the reduce-scatter of two equal partial gradients doubles this
+    rank's rows."""
+    from tcfp_b200.kernels import block_quantize_fp8
+    from tcfp_b200.nn import LayerHooks, TCFPLinear
+
+    torch.manual_seed(12)
+    plain = TCFPLinear(256, 384, bias=False, use_tensor_cores=True, **kw).to(DEV)
+    hooked = TCFPLinear(256, 384, bias=False, use_tensor_cores=True, **kw).to(DEV)
+    hooked.load_state_dict(plain.state_dict())
+    bs = kw.get("scale_block_size")
+    rows = 384
+    x_mine = acts(97, rows, 256).to(DEV)
+    x_peer = acts(98, rows, 256).to(DEV) * 3.0
+    calls = []
+
+    class Handle:
+        waited = False
+
+        def wait(self):
+            Handle.waited = True
+
+    class TwoRanks:
+        def gather_rows(self, t):
+            calls.append(("rows", t.dtype, tuple(t.shape)))
+            if t.dtype == torch.float8_e4m3fn:
+                peer, _ = block_quantize_fp8(x_peer, bs, torch.float8_e4m3fn)
+                return torch.cat([t.view(torch.uint8), peer.view(torch.uint8)]).view(t.dtype)
+            return torch.cat([t, x_peer.to(t.dtype)])
+
+        def gather_planes(self, planes):
+            calls.append(("planes", planes.dtype, tuple(planes.shape)))
+            _, peer = block_quantize_fp8(x_peer, bs, torch.float8_e4m3fn)
+            return torch.cat([planes, peer], dim=1)
+
+        def scatter_rows_async(self, full):
+            calls.append(("scatter", full.dtype, tuple(full.shape)))
+            assert hooked.weight.grad is None            # the weight gradient comes after
+            return Handle(), 2.0 * full[:rows]
+
+    hooked._hooks = LayerHooks(sp=TwoRanks())
+    x_full = torch.cat([x_mine, x_peer]).requires_grad_(True)
+    x_local = x_mine.clone().requires_grad_(True)
+    y_ref = plain(x_full)
+    y = hooked(x_local)
+    assert y.shape == (2 * rows, 384) and torch.equal(y, y_ref)
+    g = acts(99, 2 * rows, 384, torch.float32).to(DEV)
+    y_ref.backward(g)
+    y.backward(g)
+    assert Handle.waited and x_local.grad.shape == (rows, 256)
+    assert torch.equal(x_local.grad, 2.0 * x_full.grad[:rows])
+    assert torch.equal(hooked.weight.grad, plain.weight.grad)
+    kinds = [c[0] for c in calls]
+    if bs is None:
+        assert kinds == ["rows", "scatter"] and calls[0][1] == torch.bfloat16
+    elif kw.get("hp_grad_weight"):
+        assert kinds == ["rows", "planes", "rows", "scatter"] and calls[0][1] == torch.float8_e4m3fn
+    else:
+        assert kinds == ["rows", "planes", "scatter"] and calls[1][2] == (256 // bs, rows)
+
+
+@pytest.mark.parametrize("kw", [dict(scale_block_size=64), dict()], ids=["block64", "per_tensor"])
+def test_sequence_parallel_output_hooks_scatter_the_output_and_gather_the_gradient(kw):
+    """``LayerHooks.sp_out``: the output is reduce-scattered inside the layer
+    and the layer returns one rank's rows; backward it is handed the gradient
+    of those rows.  With block scaling it quantizes them, gathers codes and
+    exponents for dX and fetches the full-precision gradient for dW while the
+    dX GEMM is queued; with per-tensor scaling it gathers the gradient first.
+    Two equal ranks on one GPU, the peer's gradient rows quantized here."""
+    from tcfp_b200.kernels import block_quantize_fp8
+    from tcfp_b200.nn import LayerHooks, TCFPLinear
+
+    torch.manual_seed(13)
+    plain = TCFPLinear(256, 384, bias=False, use_tensor_cores=True, **kw).to(DEV)
+    hooked = TCFPLinear(256, 384, bias=False, use_tensor_cores=True, **kw).to(DEV)
+    hooked.load_state_dict(plain.state_dict())
+    bs = kw.get("scale_block_size")
+    rows = 384
+    g_mine = acts(101, rows, 384, torch.float32).to(DEV)
+    g_peer = acts(102, rows, 384, torch.float32).to(DEV) * 0.25
+    calls, handles = [], []
+
+    class Handle:
+        def __init__(self):
+            self.waited = False
+            handles.append(self)
+
+        def wait(self):
+            self.waited = True
+
+    class TwoRanks:
+        def scatter_rows_async(self, full):
+            calls.append("scatter")
+            return Handle(), 2.0 * full[:rows]
+
+        def gather_rows(self, t):
+            calls.append(("rows", t.dtype))
+            if t.dtype == torch.float8_e5m2:
+                peer, _ = block_quantize_fp8(g_peer, bs, torch.float8_e5m2)
+                return torch.cat([t.view(torch.uint8), peer.view(torch.uint8)]).view(t.dtype)
+            return torch.cat([t, g_peer])
+
+        def gather_planes(self, planes):
+            calls.append("planes")
+            _, peer = block_quantize_fp8(g_peer, bs, torch.float8_e5m2)
+            return torch.cat([planes, peer], dim=1)
+
+        def gather_rows_async(self, t):
+            calls.append(("rows_async", t.dtype))
+            return Handle(), torch.cat([t, g_peer])
+
+    hooked._hooks = LayerHooks(sp_out=TwoRanks())
+    x1 = acts(100, 2 * rows, 256).to(DEV).requires_grad_(True)
+    x2 = x1.detach().clone().requires_grad_(True)
+    y_ref = plain(x1)
+    y = hooked(x2)
+    assert y.shape == (rows, 384) and torch.equal(y, 2.0 * y_ref[:rows])
+    y_ref.backward(torch.cat([g_mine, g_peer]))
+    y.backward(g_mine)
+    assert all(h.waited for h in handles)
+    assert torch.equal(x2.grad, x1.grad) and torch.equal(hooked.weight.grad, plain.weight.grad)
+    if bs is None:
+        assert calls == ["scatter", ("rows", torch.float32)]
+    else:
+        assert calls == ["scatter", ("rows", torch.float8_e5m2), "planes", ("rows_async", torch.float32)]
 
 
 def test_error_feedback_snapshot_does_not_stop_training(tmp_path):

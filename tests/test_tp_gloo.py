@@ -95,6 +95,19 @@ def _worker(rank: int, world: int, port: int, ret):
         ok &= ya.shape == (8, a1 - a0) and torch.allclose(ya, ref_a(x)[:, a0:a1], atol=1e-5)
         ok &= torch.allclose(yb, ref_b(x)[:, b0:b1], atol=1e-5)
         ok &= torch.allclose(xf.grad, xg.grad, atol=1e-4)                       # one all-reduce for the whole group
+        # the collectives of the fused sequence-parallel form (FP8 codes as bytes, exponent planes, reduce-scatter)
+        from tcfp_b200.tp import SequenceParallelIO
+
+        io = SequenceParallelIO()
+        codes = [(torch.randn(4, 16, generator=torch.Generator().manual_seed(r))).to(torch.float8_e4m3fn) for r in range(world)]
+        got = io.gather_rows(codes[rank])
+        ok &= got.dtype == torch.float8_e4m3fn and torch.equal(got.view(torch.uint8), torch.cat(codes).view(torch.uint8))
+        planes = [(torch.arange(6).reshape(2, 3) + 10 * r).to(torch.int8) for r in range(world)]
+        ok &= torch.equal(io.gather_planes(planes[rank]), torch.cat(planes, dim=1))
+        handle, mine = io.scatter_rows_async(torch.full((4, 3), float(rank + 1)))
+        if handle is not None:
+            handle.wait()
+        ok &= mine.shape == (2, 3) and torch.equal(mine, torch.full((2, 3), 3.0))
         # a token count the world size does not divide is refused, not truncated
         try:
             sp.down(torch.randn(3, e - s))
