@@ -52,12 +52,13 @@ class HostStreamedLinear:
         assert K == self.weight.shape[1] and out_host.shape == (M, self.weight.shape[0])
         cur = torch.cuda.current_stream()
         x_dev, y_dev = self._buffers(x_host)
-        w_hi, w_lo, s_hi, s_lo = fused_dual_quantize_fp8(self.weight, self.bs, self.err)
-        rows = -(-M // self.chunks)
-        rows = -(-rows // 128) * 128
+        # the uploads start with the call: they do not depend on the weight quantizer queued next
         start_ev = torch.cuda.Event()
         start_ev.record(cur)
         self._s_up.wait_event(start_ev)
+        w_hi, w_lo, s_hi, s_lo = fused_dual_quantize_fp8(self.weight, self.bs, self.err)
+        rows = -(-M // self.chunks)
+        rows = -(-rows // 128) * 128
         for c in range(self.chunks):
             r0, r1 = c * rows, min(M, (c + 1) * rows)
             if r0 >= r1:
