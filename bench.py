@@ -405,7 +405,12 @@ def _kernel_extras(dev, timed) -> dict:
     out["block64_dx_total_first_use"] = {"ms": out["block64_dx_gemm_weight_retargeted"]["ms"] + ms}
     gemm("block64_dx_exact_bf16_route", lambda: fused_block_scaled_backward_dx(gq, hi, lo, sg, sh, sl, 64, exact_bf16=True))
     xb = block_dequantize_bf16(a, sa, 64)
-    gemm("block64_dw_bf16_head_tail", lambda: bf16_weight_grad(gy, xb), 2.0 * n**3)
+    gemm("block64_dw_f32_gradient_bf16_head_tail", lambda: bf16_weight_grad(gy, xb), 2.0 * n**3)
+    gyb = gy.to(torch.bfloat16)
+    gemm("block64_dw_bf16_gradient", lambda: bf16_weight_grad(gyb, xb), 2.0 * n**3)
+    ms = timed(lambda: block_dequantize_bf16(a, sa, 64), iters, 3) / iters
+    out["block64_dequantize_saved_activation"] = {"us": ms * 1e3, "algorithmic_bytes_per_elem": 3, "gbs": 3.0 * e / ms / 1e6,
+                                                  "frac_of_hbm": 3.0 * e / ms / 1e6 / hbm}
     pa, ia = to_fp8_e4m3(x)
     pg, ig = to_fp8_e5m2(gy)
     gemm("per_tensor_dw_fp8", lambda: fp8_weight_grad(pg, pa, ig, ia), 2.0 * n**3)

@@ -179,6 +179,14 @@ int32_t tcfp_block_dequantize_bf16(const uint8_t* codes, const int8_t* exps,
                                    int32_t block_size, int32_t fmt,
                                    int32_t sentinel_zero, void* stream);
 
+/* FP32 -> bf16 head + bf16 tail (x = head + tail to 16 significant bits:
+ * head = bf16(x), tail = bf16(x - head)), the operand form tcfp_bf16_dw_gemm
+ * takes for an FP32 gradient.  n elements, n % 4 == 0.  No reference
+ * counterpart: the reference multiplies the FP32 gradient as it is
+ * (tcfp/nn/__init__.py:744-750). */
+int32_t tcfp_split_bf16(const float* x, void* head_bf16, void* tail_bf16,
+                        int64_t n, void* stream);
+
 /* ---- K3: fused dual GEMM ----------------------------------------------- */
 /*
  * Per-tensor scaled.  trans_b == 0 (forward, "NT"):

@@ -40,6 +40,7 @@ _SIGNATURES = {
     "tcfp_pack_scales": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_int32, c_void_p]),
     "tcfp_block_dequantize_bf16": (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int32, c_int32,
                                              c_int32, c_void_p]),
+    "tcfp_split_bf16": (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
     "tcfp_dual_gemm": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_int32, c_int64, c_int64, c_int64, c_int32, c_void_p]),
     "tcfp_dw_gemm": (c_int32, [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_int64,

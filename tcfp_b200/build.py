@@ -65,10 +65,13 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             print(" ".join(cmd), flush=True)
         subprocess.run(cmd, check=True)
         objs.append(str(obj))
-    cmd = [nvcc, *ARCH, "-shared", "-o", str(LIB), *objs, "-cudart", "static"]
+    # link under a temporary name and rename: a reader never sees a half-written library
+    tmp = LIB.with_name(LIB.name + ".tmp")
+    cmd = [nvcc, *ARCH, "-shared", "-o", str(tmp), *objs, "-cudart", "static"]
     if verbose:
         print(" ".join(cmd), flush=True)
     subprocess.run(cmd, check=True)
+    tmp.replace(LIB)
     return LIB
 
 

@@ -149,6 +149,21 @@ def fp8_weight_grad(grad_fp8, act_fp8, grad_inv, act_inv, *, out_dtype=torch.flo
     return out
 
 
+def split_bf16(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """FP32 tensor -> ``(head, tail)`` bf16 with ``head = bf16(x)`` and
+    ``tail = bf16(x - head)``: ``head + tail`` carries 16 significant bits of
+    ``x``.  One pass (the three torch operations it replaces move 22 B/elem)."""
+    assert x.dtype == torch.float32 and x.is_cuda
+    x = x.contiguous()
+    if x.numel() % 4 != 0:
+        head = x.to(torch.bfloat16)
+        return head, (x - head.float()).to(torch.bfloat16)
+    head = torch.empty_like(x, dtype=torch.bfloat16)
+    tail = torch.empty_like(head)
+    _C.check(_C.load().tcfp_split_bf16(_C.ptr(x), _C.ptr(head), _C.ptr(tail), x.numel(), _C.stream()))
+    return head, tail
+
+
 def bf16_weight_grad(grad: torch.Tensor, act_bf16: torch.Tensor) -> torch.Tensor:
     """``dW = grad^T @ act`` -> ``(D_out, D_in)`` FP32 for an FP32 (or bf16)
     gradient ``(M, D_out)`` and a bf16 activation ``(M, D_in)``: the gradient
@@ -165,10 +180,11 @@ def bf16_weight_grad(grad: torch.Tensor, act_bf16: torch.Tensor) -> torch.Tensor
         _C.check(_C.load().tcfp_bf16_dw_gemm(_C.ptr(grad.contiguous()), _C.ptr(act_bf16.contiguous()), None, _C.ptr(out),
                                              _C.F32, M, D_out, D_in, _C.stream()))
         return out
-    g_hi = grad.to(torch.bfloat16)
     g_lo = None
     if grad.dtype == torch.float32:
-        g_lo = (grad - g_hi.float()).to(torch.bfloat16)
+        g_hi, g_lo = split_bf16(grad)
+    else:
+        g_hi = grad.to(torch.bfloat16)
     out = torch.empty((D_in, D_out), device=grad.device, dtype=torch.float32)
     _C.check(_C.load().tcfp_bf16_dw_gemm(_C.ptr(act_bf16.contiguous()), _C.ptr(g_hi), _C.ptr(g_lo), _C.ptr(out),
                                          _C.F32, M, D_in, D_out, _C.stream()))

@@ -229,6 +229,23 @@ def test_bf16_weight_grad_is_fp32_accurate():
         assert rel_fro(out, ref) <= 2e-5
 
 
+def test_split_bf16_equals_the_three_torch_passes():
+    from tcfp_b200.kernels import split_bf16
+
+    x = acts(66, 1000, 516, torch.float32).to(DEV)
+    x[::7] *= 1e-20          # tails that underflow towards zero
+    x[1::7] *= 1e20
+    x[0, :8] = torch.tensor([0.0, -0.0, 1.0, -1.0, 3.0e38, -3.0e38, 1e-45, 2.0**-126], device=DEV)
+    head, tail = split_bf16(x)
+    want_head = x.to(torch.bfloat16)
+    want_tail = (x - want_head.float()).to(torch.bfloat16)
+    assert torch.equal(head.view(torch.int16), want_head.view(torch.int16))
+    assert torch.equal(tail.view(torch.int16), want_tail.view(torch.int16))
+    odd = x.flatten()[:1001]                       # not a multiple of 4: the torch passes
+    h2, t2 = split_bf16(odd)
+    assert torch.equal(h2, want_head.flatten()[:1001]) and torch.equal(t2, want_tail.flatten()[:1001])
+
+
 def test_bf16_weight_grad_bf16_gradient_and_bf16_layer_output():
     from tcfp_b200.kernels import bf16_weight_grad
     from tcfp_b200.nn import TCFPLinear
