@@ -1,7 +1,7 @@
 """Benchmark of the TCFP-12 hot path: block-scaled dual-FP8 GEMM at 8192^3.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload gemm|mlp|mlp_large|decoder] [--sp] [--no-extras]
+                    [--workload gemm|mlp|mlp_large|decoder] [--sp] [--no-extras] [--kernel-table]
 
 One "step" is one forward pass of the hot path over one batch: the fused
 block-scaled dual GEMM  out = X_q . W_hi^T + X_q . W_lo^T  (both products
@@ -309,7 +309,26 @@ def _build_train_workload(name: str, dev, world: int, sp: bool):
     return step, flop
 
 
-def _train_step_extra(name: str, dev, world: int, timed, steps: int, sp: bool = False) -> dict:
+def _kernel_table(step, top: int = 30) -> dict:
+    """Device time per kernel over two steps of a workload, as the torch
+    profiler records it on this rank (``--kernel-table``)."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+        for _ in range(2):
+            step()
+        torch.cuda.synchronize()
+    rows = [(e.key, e.count, e.device_time_total) for e in prof.key_averages()
+            if e.device_time_total > 0 and e.device_type.name == "CUDA"]
+    rows.sort(key=lambda r: -r[2])
+    total = sum(r[2] for r in rows)
+    return {"kernel_ms_per_step": total / 2e3, "launches_per_step": sum(r[1] for r in rows) / 2,
+            "rows": [{"kernel": k[:120], "launches_per_step": c / 2, "ms_per_step": t / 2e3, "share": t / total}
+                     for k, c, t in rows[:top]]}
+
+
+def _train_step_extra(name: str, dev, world: int, timed, steps: int, sp: bool = False, kernel_table: bool = False) -> dict:
     """One tensor-parallel training workload: ms per step with the NCCL
     collectives inside the timed region, the same step with the collectives
     switched off, and their difference (communication not hidden by compute)."""
@@ -322,6 +341,8 @@ def _train_step_extra(name: str, dev, world: int, timed, steps: int, sp: bool = 
     res = {"config": TRAIN_DESC[name], "parallelism": (f"tp{world}" + (" sequence-parallel" if sp else "")) if world > 1
            else "single GPU", "ms_per_step": ms, "steps": steps,
            "linear_tflops_effective": flop / (ms * 1e-3) / 1e12, "loss": float(step().item())}
+    if kernel_table:
+        res["kernel_table"] = _kernel_table(step)
     if world > 1:
         with tp.collectives_disabled():
             ms_nocomm = timed(step, steps, 2) / steps
@@ -434,7 +455,7 @@ def run_train_workload(args) -> None:
         dist.init_process_group("nccl", device_id=dev)
     timed = _make_timed(dev, world)
     with ClockSampler(local) as clk:
-        res = _train_step_extra(args.workload, dev, world, timed, args.steps, sp=args.sp)
+        res = _train_step_extra(args.workload, dev, world, timed, args.steps, sp=args.sp, kernel_table=args.kernel_table)
     _C.check_device_status()
     if rank == 0:
         print(json.dumps({
@@ -669,6 +690,8 @@ def main() -> None:
     ap.add_argument("--workload", default="gemm", choices=["gemm", "mlp", "mlp_large", "decoder"])
     ap.add_argument("--sp", action="store_true", help="decoder workload: sequence-parallel form")
     ap.add_argument("--no-extras", action="store_true", help="headline line only")
+    ap.add_argument("--kernel-table", action="store_true",
+                    help="with --workload: add the per-kernel device time of two steps (torch profiler) to the line")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
