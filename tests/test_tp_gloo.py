@@ -108,6 +108,21 @@ def _worker(rank: int, world: int, port: int, ret):
         if handle is not None:
             handle.wait()
         ok &= mine.shape == (2, 3) and torch.equal(mine, torch.full((2, 3), 3.0))
+        # measurement aid: layers built under single_rank() are unsharded and, with the collectives off, compute
+        # the single-GPU form of the model inside a multi-rank job
+        from tcfp_b200 import tp as tpmod
+
+        with tpmod.single_rank():
+            whole = ParallelMLP(d, h, granule=granule, layer_factory=factory)
+        ok &= whole.up.inner.weight.shape == (h, d) and whole.down.inner.weight.shape == (d, h)
+        with torch.no_grad():
+            whole.up.inner.weight.copy_(ref_up.weight)
+            whole.up.inner.bias.copy_(ref_up.bias)
+            whole.down.inner.weight.copy_(ref_down.weight)
+            whole.down.bias.copy_(ref_down.bias)
+        with tpmod.collectives_disabled():
+            ok &= torch.allclose(whole(x), y_ref, atol=1e-5)
+        ok &= tpmod.world_and_rank() == (world, rank)
         # a token count the world size does not divide is refused, not truncated
         try:
             sp.down(torch.randn(3, e - s))
