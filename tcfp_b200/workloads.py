@@ -10,8 +10,8 @@ import torch.distributed as dist
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .tp import (ColumnParallelLinear, ParallelMLP, RowParallelLinear, gather_from_sequence_parallel,
-                 world_and_rank)
+from .tp import (ColumnParallelLinear, ParallelMLP, RowParallelLinear, copy_to_parallel,
+                 gather_from_sequence_parallel, world_and_rank)
 
 
 def _world() -> int:
@@ -19,13 +19,19 @@ def _world() -> int:
 
 
 class RMSNorm(nn.Module):
-    def __init__(self, d: int, eps: float = 1e-5):
+    """``token_sharded=True``: every rank normalises its own tokens, so the
+    gradient of the (replicated) weight is a partial sum and is all-reduced on
+    the way back -- otherwise the ranks' copies of the weight drift apart."""
+
+    def __init__(self, d: int, eps: float = 1e-5, token_sharded: bool = False):
         super().__init__()
         self.weight = nn.Parameter(torch.ones(d))
         self.eps = eps
+        self.token_sharded = token_sharded
 
     def forward(self, x):
-        return F.rms_norm(x, (x.shape[-1],), self.weight.to(x.dtype), self.eps)
+        w = copy_to_parallel(self.weight) if self.token_sharded else self.weight
+        return F.rms_norm(x, (x.shape[-1],), w.to(x.dtype), self.eps)
 
 
 class DecoderLayer(nn.Module):
@@ -53,12 +59,12 @@ class DecoderLayer(nn.Module):
         self.head_dim = d_model // n_heads
         self.heads_local = n_heads // world
         g_attn = max(granule, self.head_dim)
-        self.norm1 = RMSNorm(d_model)
+        self.norm1 = RMSNorm(d_model, token_sharded=self.sp)
         self.qkv = ColumnParallelLinear(d_model, (d_model, d_model, d_model), bias=False, granule=g_attn,
                                         sequence_parallel=self.sp, **layer_kw)
         self.o = RowParallelLinear(d_model, d_model, bias=False, granule=g_attn, reduce_dtype=torch.bfloat16,
                                    sequence_parallel=self.sp, overlap_chunks=overlap_chunks, **layer_kw)
-        self.norm2 = RMSNorm(d_model)
+        self.norm2 = RMSNorm(d_model, token_sharded=self.sp)
         self.gate_up = ColumnParallelLinear(d_model, (ffn, ffn), bias=False, granule=granule,
                                             sequence_parallel=self.sp, **layer_kw)
         self.down = RowParallelLinear(ffn, d_model, bias=False, granule=granule, reduce_dtype=torch.bfloat16,

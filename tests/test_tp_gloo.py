@@ -123,6 +123,13 @@ def _worker(rank: int, world: int, port: int, ret):
         with tpmod.collectives_disabled():
             ok &= torch.allclose(whole(x), y_ref, atol=1e-5)
         ok &= tpmod.world_and_rank() == (world, rank)
+        # a norm applied to token shards: the replicated weight's gradient is summed over the ranks
+        from tcfp_b200.workloads import RMSNorm
+
+        whole_norm, shard_norm = RMSNorm(d), RMSNorm(d, token_sharded=True)
+        (whole_norm(x) * target).sum().backward()
+        (shard_norm(x[rank * rows:(rank + 1) * rows]) * target[rank * rows:(rank + 1) * rows]).sum().backward()
+        ok &= torch.allclose(shard_norm.weight.grad, whole_norm.weight.grad, atol=1e-5)
         # a token count the world size does not divide is refused, not truncated
         try:
             sp.down(torch.randn(3, e - s))
