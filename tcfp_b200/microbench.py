@@ -113,6 +113,20 @@ def qvar(n: int) -> None:
         print(f"{name:<34s} {ms * 1e3:8.1f} us  {6 * e / ms / 1e6:7.0f} GB/s (6 B/elem algorithmic)")
 
 
+def ptq(n: int) -> None:
+    """Per-tensor dual quantizer with fresh scales (three dependent passes) on an
+    n x n/2 weight with its error buffer: the case to capture under ncu for the
+    DRAM bytes each pass really moves."""
+    from .core import dual_quantize_per_tensor
+
+    w = torch.randn(n, n // 2, device=DEV) * 0.02
+    err = torch.zeros_like(w)
+    e = w.numel()
+    ms = timeit(lambda: dual_quantize_per_tensor(w, err), iters=5, warmup=2)
+    print(f"dual_quantize per-tensor EF fresh scales {n}x{n // 2}: {ms * 1e3:.1f} us  {14 * e / ms / 1e6:.0f} GB/s "
+          f"(14 B/elem algorithmic; W + e = {8 * e / 1e6:.0f} MB)")
+
+
 def dx(n: int) -> None:
     from .kernels import block_quantize_fp8, block_retarget, fused_block_scaled_backward_dx, fused_dual_quantize_fp8
 
@@ -178,4 +192,4 @@ def lib(n: int) -> None:
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     size = int(sys.argv[2]) if len(sys.argv) > 2 else 8192
-    {"gemm": gemm, "block": block, "quant": quant, "lib": lib, "qvar": qvar, "dx": dx, "actq": actq, "dw": dw}[what](size)
+    {"gemm": gemm, "block": block, "quant": quant, "lib": lib, "qvar": qvar, "dx": dx, "actq": actq, "dw": dw, "ptq": ptq}[what](size)
