@@ -540,6 +540,39 @@ def run_reference(args) -> None:
     print(json.dumps(line), flush=True)
 
 
+def _parse_cpulist(text: str) -> set[int]:
+    cpus: set[int] = set()
+    for part in text.strip().split(","):
+        if not part:
+            continue
+        lo, _, hi = part.partition("-")
+        cpus.update(range(int(lo), int(hi or lo) + 1))
+    return cpus
+
+
+def _bind_near_gpu(index: int):
+    """Multi-rank runs: restrict this process to the CPUs of its GPU's NUMA
+    node (sysfs ``local_cpulist`` of the GPU's PCI function) BEFORE the pinned
+    host buffers are allocated, so that they land in the memory next to the
+    GPU's PCIe root instead of wherever the launcher started the process.
+    Returns the CPU list applied, or None when there is nothing to do."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        bus = pynvml.nvmlDeviceGetPciInfo(pynvml.nvmlDeviceGetHandleByIndex(index)).busId
+        bus = (bus.decode() if isinstance(bus, bytes) else bus).lower()[-12:]
+        text = Path(f"/sys/bus/pci/devices/{bus}/local_cpulist").read_text().strip()
+        allowed = os.sched_getaffinity(0)
+        want = _parse_cpulist(text) & allowed
+        if want and want != allowed:
+            os.sched_setaffinity(0, want)
+            return text
+    except Exception:
+        pass
+    return None
+
+
 def run_ours(args) -> None:
     import torch
     import torch.distributed as dist
@@ -554,6 +587,7 @@ def run_ours(args) -> None:
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     _C.load()  # no library, no benchmark
+    cpu_binding = _bind_near_gpu(local) if world > 1 else None
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
@@ -633,7 +667,7 @@ def run_ours(args) -> None:
                       "ms_times_mhz": (sus_ms * sus_clk["sm_mhz"]) if sus_clk["sm_mhz"] else None,
                       "frac_of_2x_bf16_sustained": FLOP_PER_STEP / sus_ms / 1e9 / (2.0 * peaks["bf16_sustained"])},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 4,
-                "ms_per_step": e2e_ms / e2e_steps,
+                "ms_per_step": e2e_ms / e2e_steps, "host_cpus": cpu_binding,
                 "path": "HostStreamedLinear.forward_from_host: pinned host X -> H2D -> fused_dual_quantize_fp8(W, EF) -> "
                         f"block_quantize_fp8(X) -> dual GEMM -> D2H out, in {E2E_CHUNKS} row chunks on 3 streams"},
         "gpu_launches": launches_per_step * args.steps,
