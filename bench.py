@@ -328,7 +328,8 @@ def _kernel_table(step, top: int = 30) -> dict:
                      for k, c, t in rows[:top]]}
 
 
-def _train_step_extra(name: str, dev, world: int, timed, steps: int, sp: bool = False, kernel_table: bool = False) -> dict:
+def _train_step_extra(name: str, dev, world: int, timed, steps: int, sp: bool = False, kernel_table: bool = False,
+                      single_ms: float | None = None) -> dict:
     """One tensor-parallel training workload: ms per step with the NCCL
     collectives inside the timed region, the same step with the collectives
     switched off, and their difference (communication not hidden by compute)."""
@@ -351,14 +352,16 @@ def _train_step_extra(name: str, dev, world: int, timed, steps: int, sp: bool = 
         res["collective"] = "NCCL all-reduce (bf16/fp32 partial outputs forward, input gradients backward)" if not sp \
             else "NCCL all-gather (FP8 codes forward, bf16 gradients backward) + reduce-scatter"
         # the single-GPU form of the same step, every rank running its own copy at the same time on this box
-        del step
-        torch.cuda.empty_cache()
-        with tp.single_rank():
-            step, _ = _build_train_workload(name, dev, 1, False)
-        with tp.collectives_disabled():
-            ms_single = timed(step, steps, 2) / steps
-        res["ms_per_step_single_gpu"] = ms_single
-        res["efficiency_vs_n1"] = ms_single / (world * ms)
+        # (``single_ms``: already measured in this run for the same workload)
+        if single_ms is None:
+            del step
+            torch.cuda.empty_cache()
+            with tp.single_rank():
+                step, _ = _build_train_workload(name, dev, 1, False)
+            with tp.collectives_disabled():
+                single_ms = timed(step, steps, 2) / steps
+        res["ms_per_step_single_gpu"] = single_ms
+        res["efficiency_vs_n1"] = single_ms / (world * ms)
     res["peak_mem_gb"] = torch.cuda.max_memory_allocated() / 2**30
     del step
     torch.cuda.empty_cache()
@@ -698,7 +701,9 @@ def run_ours(args) -> None:
             torch.cuda.empty_cache()
         if world > 1:
             try:
-                extra["decoder_train_step_sequence_parallel"] = _train_step_extra("decoder", dev, world, timed, 3, sp=True)
+                extra["decoder_train_step_sequence_parallel"] = _train_step_extra(
+                    "decoder", dev, world, timed, 3, sp=True,
+                    single_ms=extra.get("decoder_train_step", {}).get("ms_per_step_single_gpu"))
             except Exception as e:
                 extra["decoder_train_step_sequence_parallel"] = {"error": repr(e)[:200]}
             torch.cuda.empty_cache()
