@@ -423,7 +423,9 @@ __global__ void pack_scales_kernel(const int8_t* __restrict__ exps, uint8_t* __r
 
 // block-scaled codes -> bf16 values.  VEC = 16: one 128-bit load of codes and
 // two 128-bit stores per thread (16 codes never straddle a scale block);
-// VEC = 4 serves arrays that are only 4-byte aligned.
+// VEC = 4 serves arrays that are only 4-byte aligned.  (Two groups per thread,
+// half the tensor apart, measured slower inside a training step: 2.39 vs 2.06 ms
+// over its 16 launches.)
 template <int BS, bool E5M2, int VEC>
 __global__ void __launch_bounds__(256)
 block_dequantize_bf16_kernel(const uint8_t* __restrict__ codes, const int8_t* __restrict__ exps,

@@ -60,39 +60,44 @@ block_retarget_kernel(const uint8_t* __restrict__ codes_hi, const uint8_t* __res
   const int64_t c0 = (int64_t)(blockIdx.x % tiles_c) * kTile;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+  // ---- the tile's codes first: 16 independent 32-bit loads per thread, in flight while the exponents are staged.
+  //      4 x 4 micro-tiles: rows 4*(warp + 8*i) .. +3, columns 4*lane .. +3
+  uint32_t raw_all[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int rw = warp + 8 * i;                 // row word: rows 4*rw .. 4*rw + 3
+#pragma unroll
+    for (int rr = 0; rr < 4; ++rr) {
+      const int64_t row = r0 + 4 * rw + rr, col = c0 + 4 * lane;
+      raw_all[i][rr] = (row < R && col < C) ? __ldg(reinterpret_cast<const uint32_t*>(codes + row * C + col)) : 0u;
+    }
+  }
+
   // ---- exponents of the tile: s[c / bs][r]; -128 marks an all-zero residual block
+  if (threadIdx.x < kColBlocks * kRowGroups) s_t[threadIdx.x / kRowGroups][threadIdx.x % kRowGroups] = -127;
+  __syncthreads();
   for (int i = threadIdx.x; i < kColBlocks * kTile; i += kThreads) {
     const int cb = i / kTile, r = i % kTile;
     const int64_t col_block = c0 / BS + cb;
     int8_t e = -128;
     if (r0 + r < R && col_block * BS < C) e = exps[col_block * R + r0 + r];
     s_e[cb][r] = e;
-  }
-  __syncthreads();
-  if (threadIdx.x < kColBlocks * kRowGroups) {
-    const int cb = threadIdx.x / kRowGroups, g = threadIdx.x % kRowGroups;
-    int t = -127;
-    for (int r = g * BS; r < (g + 1) * BS; ++r) {
-      const int e = (int)s_e[cb][r];
-      if (e != -128 && e > t) t = e;
-    }
-    s_t[cb][g] = t;
+    // a warp holds 32 consecutive rows of one column block, i.e. (part of) one group of BS rows
+    const int m = __reduce_max_sync(0xFFFFFFFFu, e == -128 ? -127 : (int)e);
+    if (lane == 0) atomicMax(&s_t[cb][r / BS], m);
   }
   __syncthreads();
 
-  // ---- 4 x 4 micro-tiles: rows 4*(warp + 8*i) .. +3, columns 4*lane .. +3
   const int cb = (4 * lane) / BS;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const int rw = warp + 8 * i;                 // row word: rows 4*rw .. 4*rw + 3
+    const int rw = warp + 8 * i;
     const int g = (4 * rw) / BS;
     const int t = s_t[cb][g];
     uint32_t w[4];
 #pragma unroll
     for (int rr = 0; rr < 4; ++rr) {
-      const int64_t row = r0 + 4 * rw + rr, col = c0 + 4 * lane;
-      uint32_t raw = 0;
-      if (row < R && col < C) raw = __ldg(reinterpret_cast<const uint32_t*>(codes + row * C + col));
+      const uint32_t raw = raw_all[i][rr];
       const int e = (int)s_e[cb][4 * rw + rr];
       const int shift = e - t;                    // <= 0 for live rows
       const float f = (e == -128 || shift < -126) ? 0.f : exp2_int(shift);
