@@ -152,8 +152,9 @@ class _ReduceFromParallel(torch.autograd.Function):
 def _all_gather_rows(x: torch.Tensor, group) -> torch.Tensor:
     world = dist.get_world_size(group)
     out = torch.empty((x.shape[0] * world,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
-    if not _COLLECTIVES_ENABLED:           # measurement aid: right shape, local rows everywhere
-        out.view(world, *x.shape).copy_(x.unsqueeze(0).expand(world, *x.shape))
+    if not _COLLECTIVES_ENABLED:           # measurement aid: right shape, only this rank's rows filled in
+        rank = dist.get_rank(group)
+        out[rank * x.shape[0]:(rank + 1) * x.shape[0]].copy_(x)
         return out
     dist.all_gather_into_tensor(out, x.contiguous(), group=group)
     return out
