@@ -349,6 +349,9 @@ def _train_step_extra(name: str, dev, world: int, timed, steps: int, sp: bool = 
             ms_nocomm = timed(step, steps, 2) / steps
         res["ms_per_step_collectives_off"] = ms_nocomm
         res["comm_ms_per_step"] = max(0.0, ms - ms_nocomm)
+        if sp:
+            res["collectives_off_note"] = ("with the collectives off the gathered tensors are filled by copies of the local "
+                                           "rows, which the real step does not pay: a lower bound on the exposed communication")
         res["collective"] = "NCCL all-reduce (bf16/fp32 partial outputs forward, input gradients backward)" if not sp \
             else "NCCL all-gather (FP8 codes forward, bf16 gradients backward) + reduce-scatter"
         # the single-GPU form of the same step, every rank running its own copy at the same time on this box
