@@ -255,7 +255,7 @@ def _all_reduce_async(t: torch.Tensor, group):
     return _Pending(dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group, async_op=True))
 
 
-class _Pending2(_Pending):
+class _PendingWithInput(_Pending):
     """A pending collective that also keeps its input alive until waited for."""
 
     def __init__(self, work, keep):
@@ -297,7 +297,7 @@ class SequenceParallelIO:
         t = t.contiguous()
         out = torch.empty((t.shape[0] * world,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
         work = dist.all_gather_into_tensor(out, t, group=self.group, async_op=True)
-        return _Pending2(work, t), out
+        return _PendingWithInput(work, t), out
 
     def gather_planes(self, planes: torch.Tensor) -> torch.Tensor:
         """``(P, rows_local)`` -> ``(P, rows)``: the row index is the fast dimension of a plane."""
@@ -326,7 +326,7 @@ class SequenceParallelIO:
         full = full.contiguous()
         out = torch.empty((rows,) + tuple(full.shape[1:]), dtype=full.dtype, device=full.device)
         work = dist.reduce_scatter_tensor(out, full, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
-        return _Pending2(work, full), out
+        return _PendingWithInput(work, full), out
 
 
 class ColumnParallelLinear(nn.Module):
