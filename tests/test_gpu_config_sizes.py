@@ -7,7 +7,9 @@ Frobenius error on a 512-row slice for the GEMMs.
 configuration 1: 4096 x 4096 per-tensor error feedback + 4096^3 forward;
 configuration 2: 8192 x 8192 with 0.1 % x50 outliers, block 32 / 64 / 128 error
                  feedback, 8192^3 forward and dX;
-configuration 3: 16384 x 4096 per-tensor stochastic residual, seed 0x5EED.
+configuration 3: 16384 x 4096 per-tensor stochastic residual, seed 0x5EED;
+configuration 4: the weight gradient of one decoder projection (32768 tokens,
+                 4096 -> 12288) from a bf16 gradient and from an FP32 one.
 """
 import pytest
 import torch
@@ -100,3 +102,25 @@ def test_per_tensor_stochastic_residual_16384x4096():
         lo, ilo = O.to_fp8_e4m3_sr(residual[r0:r1], rand, scale=s_lo)
         assert torch.equal(u8(glo[r0:r1]), u8(lo)), f"W_lo rows {r0}..{r1} differ"
         assert torch.equal(bits(gilo), bits(ilo))
+
+
+def test_block_path_weight_gradient_at_decoder_size():
+    """dW = g^T . x over 32768 tokens for the fused q/k/v projection (4096 ->
+    12288): the single bf16 product (256 x 256 tiles) for a bf16 gradient and
+    the head + tail dual product for an FP32 gradient, each checked on three
+    128 x 256 windows (first, interior across tile borders, last) against a
+    float64 product of the same operands."""
+    from tcfp_b200.kernels import bf16_weight_grad
+
+    tokens, d_out, d_in = 32768, 12288, 4096
+    g = acts(1301, tokens, d_out, torch.float32) * 0.01
+    x = acts(1302, tokens, d_in)
+    xd = x.to(DEV)
+    windows = [(0, 0), (6100, 1900), (d_out - 128, d_in - 256)]
+    for grad, tol in ((g.to(torch.bfloat16), 5e-5), (g, 5e-5)):   # FP32 accumulation over 32768 terms
+        out = bf16_weight_grad(grad.to(DEV), xd)
+        assert out.shape == (d_out, d_in)
+        for r0, c0 in windows:
+            ref = grad[:, r0:r0 + 128].double().t() @ x[:, c0:c0 + 256].double()
+            assert rel_fro(out[r0:r0 + 128, c0:c0 + 256], ref) <= tol, (grad.dtype, r0, c0)
+        del out
