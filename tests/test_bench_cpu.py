@@ -35,3 +35,11 @@ def test_roofline_traffic_is_read_from_the_kept_profile():
 
     traffic, src = bench._profiled_traffic()
     assert src == "profiles/dual_gemm_pair_mxf8_8192_bench.md" and 4.48e8 < traffic < 2e9
+
+
+def test_cpu_list_parsing_for_the_multi_rank_host_binding():
+    import bench
+
+    assert bench._parse_cpulist("0-3,8,10-11\n") == {0, 1, 2, 3, 8, 10, 11}
+    assert bench._parse_cpulist("") == set()
+    assert bench._bind_near_gpu(0) is None      # no GPU here: nothing to bind to, no exception
