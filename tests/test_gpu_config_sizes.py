@@ -112,7 +112,7 @@ def test_block_path_weight_gradient_at_decoder_size():
     float64 product of the same operands.  Tolerance: the tensor core adds each
     product block into its FP32 accumulator with truncation, a bias of about
     2^-25 per accumulation step towards zero; 32768 tokens are 2048 steps for
-    one product (measured 4e-5) and 4096 for head + tail (measured 7.6e-5).
+    one product (measured below 5e-5) and 4096 for head + tail (measured 7.6e-5).
     Short contractions meet 2e-5 (tests/test_gpu_nn.py)."""
     from tcfp_b200.kernels import bf16_weight_grad
 
