@@ -127,6 +127,23 @@ def ptq(n: int) -> None:
           f"(14 B/elem algorithmic; W + e = {8 * e / 1e6:.0f} MB)")
 
 
+def aux(n: int) -> None:
+    """The small HBM-bound kernels around the block-path backward at n x n:
+    FP32 -> bf16 head + tail, saved FP8 activation -> bf16, weight re-targeting."""
+    from .kernels import block_dequantize_bf16, block_quantize_fp8, block_retarget, fused_dual_quantize_fp8, split_bf16
+
+    e = n * n
+    g = torch.randn(n, n, device=DEV)
+    x = torch.randn(n, n, device=DEV, dtype=torch.bfloat16)
+    a, sa = block_quantize_fp8(x, 64)
+    hi, lo, sh, sl = fused_dual_quantize_fp8(torch.randn(n, n, device=DEV) * 0.02, 64)
+    for name, fn, bpe in (("split_bf16 (f32 -> bf16 head + tail)", lambda: split_bf16(g), 8),
+                          ("block_dequantize_bf16 (E4M3 block-64 -> bf16)", lambda: block_dequantize_bf16(a, sa, 64), 3),
+                          ("block_retarget block-64 (both planes)", lambda: block_retarget(hi, lo, sh, sl, 64), 4)):
+        ms = timeit(fn, iters=10, warmup=3)
+        print(f"{name:<48s} {ms * 1e3:7.1f} us  {bpe * e / ms / 1e6:6.0f} GB/s ({bpe} B/elem algorithmic)")
+
+
 def dx(n: int) -> None:
     from .kernels import block_quantize_fp8, block_retarget, fused_block_scaled_backward_dx, fused_dual_quantize_fp8
 
@@ -192,4 +209,4 @@ def lib(n: int) -> None:
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     size = int(sys.argv[2]) if len(sys.argv) > 2 else 8192
-    {"gemm": gemm, "block": block, "quant": quant, "lib": lib, "qvar": qvar, "dx": dx, "actq": actq, "dw": dw, "ptq": ptq}[what](size)
+    {"gemm": gemm, "block": block, "quant": quant, "lib": lib, "qvar": qvar, "dx": dx, "actq": actq, "dw": dw, "ptq": ptq, "aux": aux}[what](size)
